@@ -1,0 +1,146 @@
+/*
+ * okc_moe.h — C ABI of the B200 (sm_100a) NVFP4 W4A16 MoE decode step.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, allocates nothing,
+ * keeps no process-global mutable state, enqueues its work on the given CUDA stream and
+ * returns 0 or a negative okc_moe_error.  All device buffers are owned by the caller.
+ * Device-side waits are bounded; a wait that ran out is reported through the status
+ * word (okc_moe_read_status), never by a trap.
+ *
+ * The calls replace, in the reference (tech-cosmos/okc-muse-kernels), the `moe_*_launch`
+ * host wrappers that `muse_moe_w4a16/submission.py` binds through
+ * torch.utils.cpp_extension.load_inline (submission.py:5812-5859) and that its
+ * `prepare` / `kernel_fn` call (submission.py:6011, 6518).
+ */
+#ifndef OKC_MOE_H
+#define OKC_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* okc_stream_t; /* a cudaStream_t */
+
+enum okc_moe_error {
+  OKC_OK = 0,
+  OKC_ERR_BAD_PLAN = -1,     /* shape not supported (see okc_moe_plan) */
+  OKC_ERR_BAD_ARG = -2,      /* null pointer, misaligned pointer, T out of range */
+  OKC_ERR_CUDA = -3,         /* a CUDA runtime / driver call failed */
+  OKC_ERR_NO_DEVICE = -4,    /* no sm_100 device is current */
+  OKC_ERR_TIMEOUT = -5,      /* status word: a bounded device wait ran out */
+  OKC_ERR_TOO_LARGE = -6     /* size beyond a fixed capacity */
+};
+
+/*
+ * Shape of one MoE layer shard.  Mirrors the `config` dict of the reference's inputs
+ * (muse_moe_w4a16/reference.py:83-84: d_hidden, d_expert, n_experts, local_start,
+ * local_count, top_k) plus what the reference hard-codes (post-expert norm on/off)
+ * and what it lacks (a shared expert).
+ * Limits: hidden % 256 == 0, inter % 256 == 0, n_experts <= 512, top_k <= 16,
+ * 1 <= max_tokens <= 4096, shared_inter == 0 or == inter.
+ */
+typedef struct okc_moe_plan {
+  int32_t hidden;        /* H: model width of the MoE block */
+  int32_t inter;         /* I: expert intermediate width */
+  int32_t n_experts;     /* E: experts in the whole layer (router width) */
+  int32_t top_k;         /* experts per token */
+  int32_t local_start;   /* first expert held by this GPU */
+  int32_t local_count;   /* experts held by this GPU */
+  int32_t shared_inter;  /* 0, or the shared expert's intermediate width (== inter) */
+  int32_t max_tokens;    /* capacity the workspace is sized for */
+  int32_t post_norm;     /* 1: per-route RMSNorm(y*(1+w), eps 1e-8) before weighting (reference.py:88-90) */
+  int32_t reserved[7];   /* must be zero */
+} okc_moe_plan;
+
+typedef struct okc_moe_sizes {
+  uint64_t packed_w13_bytes;   /* repacked w13 of (local_count + shared) experts */
+  uint64_t packed_w2_bytes;    /* repacked w2 of the same experts */
+  uint64_t workspace_bytes;    /* scratch for one step in flight */
+  uint32_t expert_slots;       /* local_count + (shared_inter ? 1 : 0) */
+  uint32_t routes_per_token;   /* top_k + (shared_inter ? 1 : 0) */
+} okc_moe_sizes;
+
+/* Library / format version (major*100 + minor). */
+int okc_moe_version(void);
+const char* okc_moe_strerror(int code);
+
+/* Sizes of the caller-owned buffers for a plan.  Replaces the `torch.empty` sizes computed in
+ * `prepare` and `kernel_fn` (submission.py:6011-6070, 6527-6531). */
+int okc_moe_query(const okc_moe_plan* plan, okc_moe_sizes* out);
+
+/*
+ * Lossless repack of `count` experts' NVFP4 tensors into stage images, written at expert slot
+ * `first_slot` of packed_w13 / packed_w2.  w13: uint8 [count, 2I, H/2], w13_sf: e4m3 bytes
+ * [count, 2I, H/16], w2: uint8 [count, H, I/2], w2_sf: [count, H, I/16] (device pointers to the
+ * first expert to repack).  Replaces `_pack_weight` / `_pack_scales` / `_sq_pack`
+ * (submission.py:5916-5952).
+ */
+int okc_moe_repack(const okc_moe_plan* plan, const void* w13, const void* w13_sf, const void* w2,
+                   const void* w2_sf, int first_slot, int count, void* packed_w13, void* packed_w2,
+                   okc_stream_t stream);
+
+/*
+ * Router + token->expert sort.  logits: f32 [T, E] (row stride E).  Writes ids int32 [T, top_k]
+ * (global expert ids, descending logit, ties to the lowest index) and weights f32 [T, top_k]
+ * (softmax over the selected logits), and the sorted route tables inside `workspace`.
+ * Tokens [own_t0, own_t1) also get a route to the shared expert when the plan has one.
+ * Replaces `_routing` (muse_decode_layer/layer.py:374-414) and `moe_route` / `moe_routegather`
+ * (submission.py:324-368, 2236-2328).
+ */
+int okc_moe_route(const okc_moe_plan* plan, const float* logits, int T, int own_t0, int own_t1,
+                  int32_t* ids, float* weights, void* workspace, okc_stream_t stream);
+
+/* The sort alone, for callers that bring their own routing (the reference's `kernel_fn` inputs
+ * `topk_ids` / `topk_weights`, submission.py:23-48).  ids outside the local range are skipped. */
+int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weights, int T,
+                 int own_t0, int own_t1, void* workspace, okc_stream_t stream);
+
+/*
+ * The experts on the routes sorted into `workspace`: gather -> gate_up GEMM + SiLU*mul ->
+ * down GEMM (x routing weight, un-permuted) -> per-token combine.
+ * hidden: bf16 [T, H] with row stride `hidden_stride` elements.  gs13 / gs2: f32 [expert_slots].
+ * post_norm_w: bf16 [H] or NULL.  out: bf16 [T, H] when out_f32 == 0, else f32 [T, H] (the
+ * partial sum an expert-parallel reduce-scatter consumes).  Rows with no local route are zero.
+ * Replaces `moe_tk2f_launch` / `moe_twm_launch` + `moe_norm*_launch` (submission.py:5453, 5751).
+ */
+int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                    const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,
+                    int T, const void* post_norm_w, void* workspace, void* out, int out_f32,
+                    okc_stream_t stream);
+
+/* okc_moe_route followed by okc_moe_experts. */
+int okc_moe_step(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                 const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,
+                 const float* logits, int T, int own_t0, int own_t1, const void* post_norm_w,
+                 int32_t* ids, float* weights, void* workspace, void* out, int out_f32,
+                 okc_stream_t stream);
+
+/* Copies the sorted-route tables out of `workspace` for inspection (host or device pointers are
+ * NOT interchangeable: all four are device pointers; any may be NULL).  counts: int32
+ * [expert_slots]; sorted: int32 [T*routes_per_token] (route index t*routes_per_token+slot per
+ * position, -1 padded); pos: int32 [T*routes_per_token]; items: int32 [1 + 4*max_items]
+ * (n_items, then (slot, first position, rows, padded rows) per work item). */
+int okc_moe_export_sort(const okc_moe_plan* plan, const void* workspace, int T, int32_t* counts,
+                        int32_t* sorted, int32_t* pos, int32_t* items, int max_items,
+                        okc_stream_t stream);
+
+/* Dequantises one repacked matrix back to bf16 [rows, K] scaled by 2^-8 (the factor the GEMM
+ * epilogues fold into the global scale): which = 0 for w13 (rows = 2I, K = H), 1 for w2
+ * (rows = H, K = I).  A check of the repack + dequantisation arithmetic on CUDA cores. */
+int okc_moe_unpack_bf16(const okc_moe_plan* plan, const void* packed, int which, int slot,
+                        void* out_bf16, okc_stream_t stream);
+
+/* Synchronises `stream` and returns the step status kept in `workspace`: 0, or
+ * OKC_ERR_TIMEOUT with *detail = a code naming the wait that ran out. */
+int okc_moe_read_status(const void* workspace, okc_stream_t stream, int32_t* detail);
+
+/* Kernels launched by the last okc_moe_experts / okc_moe_step shape: a constant of the build. */
+int okc_moe_launches_per_step(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OKC_MOE_H */

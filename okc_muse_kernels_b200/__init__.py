@@ -1,0 +1,13 @@
+"""B200-native (sm_100a) NVFP4 W4A16 MoE decode step behind the reference's callable surface.
+
+    state = prepare(weights, MoEPlan(...))          # once: lossless repack of the NVFP4 experts
+    out = moe_step(hidden_bf16, router_logits, state)   # router + experts, bf16 [T, H]
+    out = kernel_fn(data, state)                    # the reference's entry: routing given
+
+The CUDA kernels live in csrc/ and are reached through the C ABI of include/okc_moe.h
+(libokc_moe_b200.so, built by ``python -m okc_muse_kernels_b200.build``).
+"""
+from .moe import MoEPlan, OkcError, kernel_fn, moe_step, prepare, read_status, route, sorted_routes, unpack_bf16
+
+__all__ = ["MoEPlan", "OkcError", "kernel_fn", "moe_step", "prepare", "read_status", "route", "sorted_routes",
+           "unpack_bf16"]

@@ -1,0 +1,70 @@
+"""Builds csrc/*.cu into okc_muse_kernels_b200/libokc_moe_b200.so for sm_100a with nvcc.
+
+    python -m okc_muse_kernels_b200.build            # build if sources are newer than the library
+    python -m okc_muse_kernels_b200.build --force
+
+nvcc cross-compiles without a GPU.  The library is built in-tree and loaded with ctypes; there is
+no JIT and no fallback: if the library is missing, importing the operators fails.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import os
+import shutil
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG, "csrc")
+OBJ = os.path.join(PKG, "build")
+LIB = os.path.join(PKG, "libokc_moe_b200.so")
+SOURCES = ("abi.cu", "route.cu", "repack.cu", "gemm.cu")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+
+
+def nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found")
+    return exe
+
+
+def _stale() -> bool:
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(PKG, "..", "include", "okc_moe.h")]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def _compile(src: str) -> tuple[str, str]:
+    obj = os.path.join(OBJ, src.replace(".cu", ".o"))
+    cmd = [nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
+    return obj, r.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles and links the library; returns its path."""
+    if not force and not _stale():
+        return LIB
+    os.makedirs(OBJ, exist_ok=True)
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        results = list(pool.map(_compile, SOURCES))
+    log = "\n".join(r[1] for r in results)
+    with open(os.path.join(OBJ, "ptxas.log"), "w") as f:
+        f.write(log)
+    if verbose:
+        print(log)
+    cmd = [nvcc(), "-shared", "-o", LIB, *[r[0] for r in results], "-cudart", "static"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,289 @@
+// The C ABI declared in include/okc_moe.h: argument checks, tensor-map encoding, launches.
+// No allocation, no global mutable state besides the lazily resolved driver entry point.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "format.cuh"
+#include "params.cuh"
+
+namespace okc {
+
+// ---- driver entry point for tensor-map encoding (resolved once; the pointer is immutable after)
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static std::atomic<EncodeFn> g_encode{nullptr};
+
+static EncodeFn encode_fn() {
+  EncodeFn f = g_encode.load(std::memory_order_acquire);
+  if (f) return f;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || ptr == nullptr)
+    return nullptr;
+  f = reinterpret_cast<EncodeFn>(ptr);
+  g_encode.store(f, std::memory_order_release);
+  return f;
+}
+
+// bf16 [rows, K] row-major, box = 64 elements x box_rows, 128-byte swizzle, zero fill outside.
+static bool encode_rows_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+  EncodeFn f = encode_fn();
+  if (!f) return false;
+  const cuuint64_t dims[2] = {K, rows};
+  const cuuint64_t strides[1] = {K * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return f(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int ncap_for(int T) {
+  int n = 16;
+  while (n < T && n < kChunkRows) n <<= 1;
+  return n;
+}
+
+static int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  return n;
+}
+
+static bool is_sm100() {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
+  return major == 10;
+}
+
+static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+struct Ws {
+  int32_t* meta;
+  int32_t* counts;
+  int4* items;
+  int32_t* sorted;
+  int32_t* pos;
+  float* wsorted;
+  uint16_t* xg;
+  uint16_t* inter;
+  float* y;
+};
+
+static Ws carve(void* workspace, const Geometry& g) {
+  uint8_t* b = static_cast<uint8_t*>(workspace);
+  Ws w;
+  w.meta = reinterpret_cast<int32_t*>(b + g.off_meta);
+  w.counts = reinterpret_cast<int32_t*>(b + g.off_counts);
+  w.items = reinterpret_cast<int4*>(b + g.off_items);
+  w.sorted = reinterpret_cast<int32_t*>(b + g.off_sorted);
+  w.pos = reinterpret_cast<int32_t*>(b + g.off_pos);
+  w.wsorted = reinterpret_cast<float*>(b + g.off_wsorted);
+  w.xg = reinterpret_cast<uint16_t*>(b + g.off_xg);
+  w.inter = reinterpret_cast<uint16_t*>(b + g.off_inter);
+  w.y = reinterpret_cast<float*>(b + g.off_y);
+  return w;
+}
+
+static int route_common(const okc_moe_plan* plan, const float* logits, const int32_t* ids_in, const float* wts_in,
+                        int T, int own_t0, int own_t1, int32_t* ids_out, float* wts_out, void* workspace,
+                        cudaStream_t stream) {
+  Geometry g;
+  if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  if (!workspace || !aligned(workspace, 256) || T <= 0 || T > plan->max_tokens) return OKC_ERR_BAD_ARG;
+  if (own_t0 < 0 || own_t1 < own_t0 || own_t1 > T) return OKC_ERR_BAD_ARG;
+  Ws w = carve(workspace, g);
+  RouteParams p;
+  p.logits = logits; p.ids_in = ids_in; p.wts_in = wts_in; p.ids_out = ids_out; p.wts_out = wts_out;
+  p.meta = w.meta; p.counts = w.counts; p.items = w.items; p.sorted = w.sorted; p.pos = w.pos; p.wsorted = w.wsorted;
+  p.T = T; p.E = plan->n_experts; p.k = plan->top_k; p.kk = g.kk; p.slots = g.slots;
+  p.local_start = plan->local_start; p.local_count = plan->local_count; p.has_shared = plan->shared_inter ? 1 : 0;
+  p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items;
+  return launch_route(p, stream) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+}  // namespace okc
+
+using namespace okc;
+
+extern "C" {
+
+int okc_moe_version(void) { return 100; }
+
+const char* okc_moe_strerror(int code) {
+  switch (code) {
+    case OKC_OK: return "ok";
+    case OKC_ERR_BAD_PLAN: return "plan outside the supported shapes";
+    case OKC_ERR_BAD_ARG: return "bad argument (null or misaligned pointer, token count out of range)";
+    case OKC_ERR_CUDA: return "a CUDA call failed";
+    case OKC_ERR_NO_DEVICE: return "the current device is not an sm_100 GPU";
+    case OKC_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case OKC_ERR_TOO_LARGE: return "size beyond a fixed capacity";
+    default: return "unknown error";
+  }
+}
+
+int okc_moe_launches_per_step(void) { return 5; }
+
+int okc_moe_query(const okc_moe_plan* plan, okc_moe_sizes* out) {
+  Geometry g;
+  if (!plan || !out || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  out->packed_w13_bytes = g.w13_expert_bytes * g.slots;
+  out->packed_w2_bytes = g.w2_expert_bytes * g.slots;
+  out->workspace_bytes = g.total;
+  out->expert_slots = static_cast<uint32_t>(g.slots);
+  out->routes_per_token = static_cast<uint32_t>(g.kk);
+  return OKC_OK;
+}
+
+int okc_moe_repack(const okc_moe_plan* plan, const void* w13, const void* w13_sf, const void* w2, const void* w2_sf,
+                   int first_slot, int count, void* packed_w13, void* packed_w2, okc_stream_t stream) {
+  Geometry g;
+  if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  if (!w13 || !w13_sf || !w2 || !w2_sf || !packed_w13 || !packed_w2) return OKC_ERR_BAD_ARG;
+  if (first_slot < 0 || count <= 0 || first_slot + count > g.slots) return OKC_ERR_BAD_ARG;
+  if (!aligned(w13, 16) || !aligned(w2, 16) || !aligned(packed_w13, 16) || !aligned(packed_w2, 16)) return OKC_ERR_BAD_ARG;
+  RepackParams a;
+  a.w = static_cast<const uint8_t*>(w13); a.sf = static_cast<const uint8_t*>(w13_sf);
+  a.out = static_cast<uint8_t*>(packed_w13);
+  a.rows = 2 * g.I; a.K = g.H; a.pairs = g.pairs13; a.stages = g.stages13; a.first_slot = first_slot; a.count = count;
+  a.is_w13 = 1; a.inter = g.I; a.expert_bytes = g.w13_expert_bytes;
+  if (launch_repack(a, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) return OKC_ERR_CUDA;
+  RepackParams b;
+  b.w = static_cast<const uint8_t*>(w2); b.sf = static_cast<const uint8_t*>(w2_sf);
+  b.out = static_cast<uint8_t*>(packed_w2);
+  b.rows = g.H; b.K = g.I; b.pairs = g.pairs2; b.stages = g.stages2; b.first_slot = first_slot; b.count = count;
+  b.is_w13 = 0; b.inter = g.I; b.expert_bytes = g.w2_expert_bytes;
+  if (launch_repack(b, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) return OKC_ERR_CUDA;
+  return OKC_OK;
+}
+
+int okc_moe_unpack_bf16(const okc_moe_plan* plan, const void* packed, int which, int slot, void* out_bf16,
+                        okc_stream_t stream) {
+  Geometry g;
+  if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  if (!packed || !out_bf16 || slot < 0 || slot >= g.slots || (which != 0 && which != 1)) return OKC_ERR_BAD_ARG;
+  UnpackParams u;
+  const size_t eb = which == 0 ? g.w13_expert_bytes : g.w2_expert_bytes;
+  u.packed = static_cast<const uint8_t*>(packed) + eb * slot;
+  u.out = static_cast<uint16_t*>(out_bf16);
+  u.K = which == 0 ? g.H : g.I;
+  u.pairs = which == 0 ? g.pairs13 : g.pairs2;
+  u.stages = which == 0 ? g.stages13 : g.stages2;
+  u.is_w13 = which == 0; u.inter = g.I;
+  return launch_unpack(u, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+int okc_moe_route(const okc_moe_plan* plan, const float* logits, int T, int own_t0, int own_t1, int32_t* ids,
+                  float* weights, void* workspace, okc_stream_t stream) {
+  if (!logits || !ids || !weights) return OKC_ERR_BAD_ARG;
+  return route_common(plan, logits, nullptr, nullptr, T, own_t0, own_t1, ids, weights, workspace,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weights, int T, int own_t0, int own_t1,
+                 void* workspace, okc_stream_t stream) {
+  if (!ids || !weights) return OKC_ERR_BAD_ARG;
+  return route_common(plan, nullptr, ids, weights, T, own_t0, own_t1, nullptr, nullptr, workspace,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
+                    const float* gs2, const void* hidden, int64_t hidden_stride, int T, const void* post_norm_w,
+                    void* workspace, void* out, int out_f32, okc_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  Geometry g;
+  if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  if (!packed_w13 || !packed_w2 || !gs13 || !gs2 || !hidden || !workspace || !out) return OKC_ERR_BAD_ARG;
+  if (T <= 0 || T > plan->max_tokens || hidden_stride < g.H || (hidden_stride % 8) != 0) return OKC_ERR_BAD_ARG;
+  if (!aligned(packed_w13, 16) || !aligned(packed_w2, 16) || !aligned(hidden, 16) || !aligned(workspace, 256) ||
+      !aligned(out, 16))
+    return OKC_ERR_BAD_ARG;
+  if ((plan->post_norm != 0) != (post_norm_w != nullptr)) return OKC_ERR_BAD_ARG;
+  if (post_norm_w && !aligned(post_norm_w, 8)) return OKC_ERR_BAD_ARG;
+  if (!is_sm100()) return OKC_ERR_NO_DEVICE;
+  const int sms = sm_count();
+  if (sms <= 0) return OKC_ERR_CUDA;
+  Ws w = carve(workspace, g);
+  const int R = T * g.kk;
+  const int ncap = ncap_for(T);
+
+  if (launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, stream) != cudaSuccess) return OKC_ERR_CUDA;
+
+  GemmParams a;
+  memset(&a, 0, sizeof(a));
+  const uint32_t boxes[4] = {16, 32, 64, 128};
+  for (int i = 0; i < 4; ++i)
+    if (!encode_rows_map(&a.bmap[i], w.xg, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.H), boxes[i])) return OKC_ERR_CUDA;
+  a.wpacked = static_cast<const uint8_t*>(packed_w13); a.gs = gs13; a.meta = w.meta; a.items = w.items;
+  a.pairs = g.pairs13; a.stages = g.stages13; a.expert_bytes = g.w13_expert_bytes;
+  a.ncap = ncap; a.n_stages = gemm_stages_for(ncap);
+  a.inter = w.inter; a.I = g.I; a.H = g.H;
+  if (launch_gemm(0, a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+
+  GemmParams b;
+  memset(&b, 0, sizeof(b));
+  for (int i = 0; i < 4; ++i)
+    if (!encode_rows_map(&b.bmap[i], w.inter, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.I), boxes[i])) return OKC_ERR_CUDA;
+  b.wpacked = static_cast<const uint8_t*>(packed_w2); b.gs = gs2; b.meta = w.meta; b.items = w.items;
+  b.pairs = g.pairs2; b.stages = g.stages2; b.expert_bytes = g.w2_expert_bytes;
+  b.ncap = ncap; b.n_stages = gemm_stages_for(ncap);
+  b.y = w.y; b.sorted = w.sorted; b.wsorted = w.wsorted; b.H = g.H; b.I = g.I;
+  b.weighted = plan->post_norm ? 0 : 1;
+  if (launch_gemm(1, b, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+
+  CombineParams c;
+  c.y = w.y; c.pos = w.pos; c.wsorted = w.wsorted; c.post_w = static_cast<const uint16_t*>(post_norm_w);
+  c.out = out; c.kk = g.kk; c.H = g.H; c.out_f32 = out_f32 ? 1 : 0;
+  if (launch_combine(c, T, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  return OKC_OK;
+}
+
+int okc_moe_step(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
+                 const float* gs2, const void* hidden, int64_t hidden_stride, const float* logits, int T, int own_t0,
+                 int own_t1, const void* post_norm_w, int32_t* ids, float* weights, void* workspace, void* out,
+                 int out_f32, okc_stream_t stream) {
+  int rc = okc_moe_route(plan, logits, T, own_t0, own_t1, ids, weights, workspace, stream);
+  if (rc != OKC_OK) return rc;
+  return okc_moe_experts(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, T, post_norm_w, workspace, out,
+                         out_f32, stream);
+}
+
+int okc_moe_export_sort(const okc_moe_plan* plan, const void* workspace, int T, int32_t* counts, int32_t* sorted,
+                        int32_t* pos, int32_t* items, int max_items, okc_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  Geometry g;
+  if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  if (!workspace || T <= 0 || T > plan->max_tokens) return OKC_ERR_BAD_ARG;
+  Ws w = carve(const_cast<void*>(workspace), g);
+  const size_t R = static_cast<size_t>(T) * g.kk;
+  cudaError_t e = cudaSuccess;
+  if (counts && e == cudaSuccess) e = cudaMemcpyAsync(counts, w.counts, sizeof(int32_t) * g.slots, cudaMemcpyDeviceToDevice, stream);
+  if (sorted && e == cudaSuccess) e = cudaMemcpyAsync(sorted, w.sorted, sizeof(int32_t) * R, cudaMemcpyDeviceToDevice, stream);
+  if (pos && e == cudaSuccess) e = cudaMemcpyAsync(pos, w.pos, sizeof(int32_t) * R, cudaMemcpyDeviceToDevice, stream);
+  if (items && e == cudaSuccess) {
+    const int n = max_items < g.max_items ? max_items : g.max_items;
+    e = cudaMemcpyAsync(items, w.meta + kMetaItems, sizeof(int32_t), cudaMemcpyDeviceToDevice, stream);
+    if (e == cudaSuccess && n > 0)
+      e = cudaMemcpyAsync(items + 1, w.items, sizeof(int32_t) * 4 * n, cudaMemcpyDeviceToDevice, stream);
+  }
+  return e == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+int okc_moe_read_status(const void* workspace, okc_stream_t stream_, int32_t* detail) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!workspace) return OKC_ERR_BAD_ARG;
+  int32_t host[2] = {0, 0};
+  const int32_t* meta = static_cast<const int32_t*>(workspace);
+  if (cudaMemcpyAsync(host, meta + kMetaStatus, sizeof(host), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (detail) *detail = host[1];
+  return host[0];
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+// Geometry of the packed weight format, the workspace layout derived from a plan, and the
+// device-side FP4 -> BF16 dequantisation shared by the GEMM kernel and the unpack utility.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/okc_moe.h"
+#include "ptx.cuh"
+
+namespace okc {
+
+constexpr int kTileRows = 128;                 // rows of one weight tile = M of one tcgen05.mma
+constexpr int kStageK = 256;                   // K elements per shared-memory stage
+constexpr int kChunkK = 32;                    // K elements one thread dequantises per tcgen05.st
+constexpr int kChunks = kStageK / kChunkK;     // 8
+constexpr int kTileCodeBytes = kChunks * kTileRows * 16;   // 16384
+constexpr int kTileScaleBytes = kChunks * kTileRows * 2;   // 2048
+constexpr int kTileBytes = kTileCodeBytes + kTileScaleBytes;
+constexpr int kStageBytes = 2 * kTileBytes;    // 36864: two tiles (gate+up, or two row tiles of w2)
+constexpr int kChunkRows = 128;                // most rows (tokens) of one work item
+constexpr int kMaxSlots = 513;                 // 512 experts + shared
+constexpr int kMaxRoutes = 16384;              // routes (tokens x routes per token) one step may hold
+
+constexpr uint32_t kOutMask = 0x81C081C0u;     // sign + 3 magnitude bits of both bf16 halves
+constexpr uint32_t kLeftMask = 0x60306030u;    // bits of w0 its three rotations leave over
+
+// meta words at the start of the workspace
+enum MetaWord { kMetaItems = 0, kMetaLocalRoutes = 1, kMetaStatus = 2, kMetaDetail = 3, kMetaTokens = 4, kMetaWords = 64 };
+
+struct Geometry {
+  int H, I, slots, kk, T, R, Rpad;
+  int pairs13, stages13, pairs2, stages2;
+  size_t w13_expert_bytes, w2_expert_bytes;
+  int max_items;
+  // workspace byte offsets
+  size_t off_meta, off_counts, off_items, off_sorted, off_pos, off_wsorted, off_xg, off_inter, off_y, total;
+};
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Fills g from a plan.  Returns false if the plan is outside the supported shapes.
+inline bool make_geometry(const okc_moe_plan& p, Geometry& g) {
+  if (p.hidden <= 0 || p.inter <= 0 || p.hidden % 256 || p.inter % 256) return false;
+  if (p.n_experts <= 0 || p.n_experts > 512 || p.top_k <= 0 || p.top_k > 16 || p.top_k > p.n_experts) return false;
+  if (p.local_start < 0 || p.local_count <= 0 || p.local_start + p.local_count > p.n_experts) return false;
+  if (p.shared_inter != 0 && p.shared_inter != p.inter) return false;
+  if (p.max_tokens <= 0 || p.max_tokens > 4096) return false;
+  if (p.post_norm != 0 && p.post_norm != 1) return false;
+  for (int i = 0; i < 7; ++i)
+    if (p.reserved[i] != 0) return false;
+  g.H = p.hidden;
+  g.I = p.inter;
+  g.slots = p.local_count + (p.shared_inter ? 1 : 0);
+  g.kk = p.top_k + (p.shared_inter ? 1 : 0);
+  g.T = p.max_tokens;
+  g.R = g.T * g.kk;
+  if (g.R > kMaxRoutes) return false;
+  g.Rpad = g.R + kChunkRows;
+  g.pairs13 = g.I / kTileRows;
+  g.stages13 = g.H / kStageK;
+  g.pairs2 = g.H / (2 * kTileRows);
+  g.stages2 = g.I / kStageK;
+  g.w13_expert_bytes = static_cast<size_t>(g.pairs13) * g.stages13 * kStageBytes;
+  g.w2_expert_bytes = static_cast<size_t>(g.pairs2) * g.stages2 * kStageBytes;
+  g.max_items = g.slots + g.R / kChunkRows + 1;
+  size_t o = 0;
+  g.off_meta = o;     o = align_up(o + kMetaWords * 4, 256);
+  g.off_counts = o;   o = align_up(o + static_cast<size_t>(g.slots + 1) * 4, 256);
+  g.off_items = o;    o = align_up(o + static_cast<size_t>(g.max_items) * 16, 256);
+  g.off_sorted = o;   o = align_up(o + static_cast<size_t>(g.R) * 4, 256);
+  g.off_pos = o;      o = align_up(o + static_cast<size_t>(g.R) * 4, 256);
+  g.off_wsorted = o;  o = align_up(o + static_cast<size_t>(g.R) * 4, 256);
+  g.off_xg = o;       o = align_up(o + static_cast<size_t>(g.Rpad) * g.H * 2, 1024);
+  g.off_inter = o;    o = align_up(o + static_cast<size_t>(g.Rpad) * g.I * 2, 1024);
+  g.off_y = o;        o = align_up(o + static_cast<size_t>(g.R) * g.H * 4, 1024);
+  g.total = o;
+  return true;
+}
+
+#ifdef __CUDACC__
+// Two E4M3 scale bytes (low byte = block 0) -> bf16x2 {scale0, scale1} * 2^118.
+// byte << 4 is the bf16 whose value is e4m3 * 2^-120 (normal and subnormal codes alike); two
+// exact multiplies bring it to e4m3 * 2^118 (<= 448 * 2^118, finite in bf16).
+__device__ __forceinline__ uint32_t scale_pair_bf16(uint32_t two_bytes) {
+  uint32_t s = ((two_bytes & 0xFFu) | ((two_bytes & 0xFF00u) << 8)) << 4;
+  s = mul_bf16x2(s, 0x7F007F00u);   // * 2^127
+  return mul_bf16x2(s, 0x77007700u);   // * 2^111
+}
+
+// One 16-code block (w0, w1) and its scale (bf16 broadcast to both halves) -> eight bf16x2
+// registers holding code * scale * 2^-8, K-ordered (register i = elements 2i, 2i+1).
+__device__ __forceinline__ void dequant_block(uint32_t w0, uint32_t w1, uint32_t sc, uint32_t* out) {
+  const uint32_t u = (w0 & kLeftMask) | (w1 & ~kLeftMask);
+  out[0] = mul_bf16x2(w0 & kOutMask, sc);
+  out[1] = mul_bf16x2(rotr32(w0, 4) & kOutMask, sc);
+  out[2] = mul_bf16x2(rotr32(w0, 10) & kOutMask, sc);
+  out[3] = mul_bf16x2(rotr32(w1, 2) & kOutMask, sc);
+  out[4] = mul_bf16x2(rotr32(w1, 6) & kOutMask, sc);
+  out[5] = mul_bf16x2(rotr32(w1, 12) & kOutMask, sc);
+  out[6] = mul_bf16x2(rotr32(u, 8) & kOutMask, sc);
+  out[7] = mul_bf16x2(rotr32(u, 14) & kOutMask, sc);
+}
+
+// One 32-code chunk (four words, two scale bytes) -> sixteen bf16x2 registers.
+__device__ __forceinline__ void dequant_chunk(const uint4& w, uint32_t two_scale_bytes, uint32_t (&out)[16]) {
+  const uint32_t s = scale_pair_bf16(two_scale_bytes);
+  const uint32_t s0 = __byte_perm(s, s, 0x1010);
+  const uint32_t s1 = __byte_perm(s, s, 0x3232);
+  dequant_block(w.x, w.y, s0, out);
+  dequant_block(w.z, w.w, s1, out + 8);
+}
+#endif
+
+}  // namespace okc

@@ -1,0 +1,75 @@
+// Kernel parameter blocks and host launchers shared by the translation units of the library.
+#pragma once
+#include "format.cuh"
+
+namespace okc {
+
+struct RouteParams {
+  const float* logits;
+  const int32_t* ids_in;
+  const float* wts_in;
+  int32_t* ids_out;
+  float* wts_out;
+  int32_t* meta;
+  int32_t* counts;
+  int4* items;
+  int32_t* sorted;
+  int32_t* pos;
+  float* wsorted;
+  int T, E, k, kk, slots, local_start, local_count, has_shared, own_t0, own_t1, max_items;
+};
+cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
+cudaError_t launch_gather(const void* hidden, int64_t stride, const int32_t* meta, const int32_t* sorted, int kk,
+                          int H, int R, void* xg, cudaStream_t stream);
+
+struct RepackParams {
+  const uint8_t* w;
+  const uint8_t* sf;
+  uint8_t* out;
+  int rows, K, pairs, stages, first_slot, count, is_w13, inter;
+  size_t expert_bytes;
+};
+cudaError_t launch_repack(const RepackParams& p, cudaStream_t stream);
+struct UnpackParams {
+  const uint8_t* packed;
+  uint16_t* out;
+  int K, pairs, stages, is_w13, inter;
+};
+cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t stream);
+
+struct GemmParams {
+  CUtensorMap bmap[4];
+  const uint8_t* wpacked;
+  const float* gs;
+  const int32_t* meta;
+  const int4* items;
+  int pairs;
+  int stages;
+  size_t expert_bytes;
+  int n_stages;
+  int ncap;
+  uint16_t* inter;
+  int I;
+  float* y;
+  const int32_t* sorted;
+  const float* wsorted;
+  int H;
+  int weighted;
+};
+cudaError_t launch_gemm(int mode, const GemmParams& p, int grid, cudaStream_t stream);
+int gemm_stages_for(int ncap);
+
+struct CombineParams {
+  const float* y;
+  const int32_t* pos;
+  const float* wsorted;
+  const uint16_t* post_w;
+  void* out;
+  int kk, H, out_f32;
+};
+cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream);
+
+size_t route_smem_bytes(int R, int slots);
+size_t gemm_smem_bytes(int n_stages, int ncap);
+
+}  // namespace okc

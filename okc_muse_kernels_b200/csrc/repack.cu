@@ -1,0 +1,90 @@
+// Prepare-time lossless repack of NVFP4 tensors into stage images, and its inverse on CUDA cores.
+// Takes the place of the reference's torch repackers `_pack_weight`, `_pack_scales`, `_sq_pack`
+// (muse_moe_w4a16/submission.py:5916-5952); the image layout is this library's own.
+#include "params.cuh"
+
+namespace okc {
+
+// Destination bit (word * 32 + bit, inside a two-word block) of bit b of code j: entry j*4 + b.
+// Generated from the rotation plan {w0: 0,4,10; w1: 2,6,12; merged leftovers: 8,14}.
+__constant__ uint8_t kPairShift[64] = {
+    6,  7,  8,  15, 22, 23, 24, 31, 10, 11, 12, 19, 26, 27, 28, 3,  16, 17, 18, 25, 0,  1,
+    2,  9,  40, 41, 42, 49, 56, 57, 58, 33, 44, 45, 46, 53, 60, 61, 62, 37, 50, 51, 52, 59,
+    34, 35, 36, 43, 14, 47, 48, 55, 30, 63, 32, 39, 20, 21, 54, 29, 4,  5,  38, 13};
+
+
+// One thread per (expert, pair, stage, tile, chunk, row): 16 source bytes + 2 scale bytes.
+__global__ void __launch_bounds__(256) okc_repack(const RepackParams p) {
+  const size_t per_expert = static_cast<size_t>(p.pairs) * p.stages * 2 * kChunks * kTileRows;
+  const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= per_expert * p.count) return;
+  const int ex = static_cast<int>(gid / per_expert);
+  size_t r = gid - static_cast<size_t>(ex) * per_expert;
+  const int row = static_cast<int>(r % kTileRows); r /= kTileRows;
+  const int chunk = static_cast<int>(r % kChunks); r /= kChunks;
+  const int tile = static_cast<int>(r % 2); r /= 2;
+  const int stage = static_cast<int>(r % p.stages); r /= p.stages;
+  const int pair = static_cast<int>(r);
+
+  const int src_row = p.is_w13 ? (tile * p.inter + pair * kTileRows + row) : (pair * 2 * kTileRows + tile * kTileRows + row);
+  const int k0 = stage * kStageK + chunk * kChunkK;
+  const uint8_t* src = p.w + (static_cast<size_t>(ex) * p.rows + src_row) * (p.K / 2) + k0 / 2;
+  const uint8_t* ssf = p.sf + (static_cast<size_t>(ex) * p.rows + src_row) * (p.K / 16) + k0 / 16;
+  const uint4 raw = *reinterpret_cast<const uint4*>(src);
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t outw[4];
+#pragma unroll
+  for (int blk = 0; blk < 2; ++blk) {
+    const uint64_t codes = static_cast<uint64_t>(words[2 * blk]) | (static_cast<uint64_t>(words[2 * blk + 1]) << 32);
+    uint64_t o = 0;
+    for (int j = 0; j < 16; ++j)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) o |= ((codes >> (4 * j + b)) & 1ull) << kPairShift[j * 4 + b];
+    outw[2 * blk] = static_cast<uint32_t>(o);
+    outw[2 * blk + 1] = static_cast<uint32_t>(o >> 32);
+  }
+  uint8_t* img = p.out + static_cast<size_t>(p.first_slot + ex) * p.expert_bytes +
+                 (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes + static_cast<size_t>(tile) * kTileBytes;
+  *reinterpret_cast<uint4*>(img + chunk * (kTileRows * 16) + row * 16) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+  *reinterpret_cast<uint16_t*>(img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2) =
+      static_cast<uint16_t>(ssf[0]) | (static_cast<uint16_t>(ssf[1]) << 8);
+}
+
+
+__global__ void __launch_bounds__(256) okc_unpack(const UnpackParams p) {
+  const size_t total = static_cast<size_t>(p.pairs) * p.stages * 2 * kChunks * kTileRows;
+  const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= total) return;
+  size_t r = gid;
+  const int row = static_cast<int>(r % kTileRows); r /= kTileRows;
+  const int chunk = static_cast<int>(r % kChunks); r /= kChunks;
+  const int tile = static_cast<int>(r % 2); r /= 2;
+  const int stage = static_cast<int>(r % p.stages); r /= p.stages;
+  const int pair = static_cast<int>(r);
+  const uint8_t* img = p.packed + (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes +
+                       static_cast<size_t>(tile) * kTileBytes;
+  const uint4 w = *reinterpret_cast<const uint4*>(img + chunk * (kTileRows * 16) + row * 16);
+  const uint32_t sc = *reinterpret_cast<const uint16_t*>(img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2);
+  uint32_t regs[16];
+  dequant_chunk(w, sc, regs);
+  const int dst_row = p.is_w13 ? (tile * p.inter + pair * kTileRows + row) : (pair * 2 * kTileRows + tile * kTileRows + row);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(p.out + static_cast<size_t>(dst_row) * p.K + stage * kStageK + chunk * kChunkK);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) dst[i] = regs[i];
+}
+
+cudaError_t launch_repack(const RepackParams& p, cudaStream_t stream) {
+  const size_t total = static_cast<size_t>(p.pairs) * p.stages * 2 * kChunks * kTileRows * p.count;
+  const size_t blocks = (total + 255) / 256;
+  if (blocks == 0) return cudaSuccess;
+  okc_repack<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t stream) {
+  const size_t total = static_cast<size_t>(p.pairs) * p.stages * 2 * kChunks * kTileRows;
+  okc_unpack<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace okc

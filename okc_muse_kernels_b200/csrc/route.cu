@@ -1,0 +1,252 @@
+// Router (softmax top-k) and token -> expert sort, one CTA per step.
+//
+// Behaviour follows the reference's routing + sort kernels (different algorithm, same results):
+//   * top-k with ties to the lowest index       muse_decode_layer/layer.py:394-406 (_routing)
+//   * local-expert filter, histogram, offsets   muse_moe_w4a16/submission.py:324-368 (moe_route)
+//   * stable (expert, route index) order        muse_moe_w4a16/submission.py:2236-2328 (moe_routegather)
+//   * active experts by load, heaviest first    muse_moe_w4a16/submission.py:345-350
+// The order inside an expert is deterministic (the reference's moe_route fills it with atomics).
+#include "params.cuh"
+
+namespace okc {
+
+
+constexpr int kRouteThreads = 1024;
+constexpr int kRouteWarps = kRouteThreads / 32;
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RouteParams p) {
+  extern __shared__ int32_t sm[];
+  const int R = p.T * p.kk;
+  // shared memory: rexp int32 [R] (local expert slot or -1) | whist int32 [32][slots] | order int32 [slots]
+  // | cnt int32 [slots+1] | offs int32 [slots+1] | ibase int32 [slots+1]
+  int32_t* rexp = sm;
+  int32_t* whist = rexp + R;
+  int32_t* order = whist + kRouteWarps * p.slots;
+  int32_t* cnt = order + p.slots;
+  int32_t* offs = cnt + p.slots + 1;
+  int32_t* ibase = offs + p.slots + 1;
+  __shared__ int s_nact;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_nact = 0;
+
+  for (int i = tid; i < kRouteWarps * p.slots; i += kRouteThreads) whist[i] = 0;
+  for (int i = tid; i < R; i += kRouteThreads) p.sorted[i] = -1;
+
+  // ---- 1. top-k (one warp per token) or load of the given ids
+  if (p.logits != nullptr) {
+    const int per = (p.E + 31) >> 5;    // candidates per lane, <= 16
+    for (int t = warp; t < p.T; t += kRouteWarps) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int e = lane + 32 * j;
+        float x = (j < per && e < p.E) ? p.logits[static_cast<size_t>(t) * p.E + e] : -INFINITY;
+        v[j] = (x == x) ? x : -INFINITY;   // NaN never wins
+      }
+      uint32_t taken = 0;
+      float my_val = 0.f;
+      int my_id = 0;
+      for (int r = 0; r < p.k; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int e = lane + 32 * j;
+          if (j < per && e < p.E && !((taken >> j) & 1u) && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        if (lane == r) { my_val = bv; my_id = bi; }
+      }
+      const float top = __shfl_sync(0xffffffffu, my_val, 0);
+      float ex = (lane < p.k) ? expf(my_val - top) : 0.f;
+      float sum = ex;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane < p.k) {
+        const float w = ex / sum;
+        p.ids_out[t * p.k + lane] = my_id;
+        p.wts_out[t * p.k + lane] = w;
+        const int le = my_id - p.local_start;
+        rexp[t * p.kk + lane] = (le >= 0 && le < p.local_count) ? le : -1;
+      }
+    }
+  } else {
+    for (int i = tid; i < p.T * p.k; i += kRouteThreads) {
+      const int t = i / p.k, s = i - t * p.k;
+      const int le = p.ids_in[i] - p.local_start;
+      rexp[t * p.kk + s] = (le >= 0 && le < p.local_count) ? le : -1;
+    }
+  }
+  if (p.has_shared)
+    for (int t = tid; t < p.T; t += kRouteThreads)
+      rexp[t * p.kk + p.k] = (t >= p.own_t0 && t < p.own_t1) ? p.local_count : -1;
+  __syncthreads();
+
+  // ---- 2. per-warp histograms over contiguous chunks of the route list
+  const int chunk = ((R + kRouteWarps - 1) / kRouteWarps + 31) & ~31;
+  const int r0 = warp * chunk;
+  for (int b = 0; b < chunk; b += 32) {
+    const int i = r0 + b + lane;
+    const int e = (i < R) ? rexp[i] : -1;
+    const uint32_t m = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && lane == (__ffs(m) - 1)) whist[warp * p.slots + e] += __popc(m);
+    __syncwarp();
+  }
+  __syncthreads();
+  // exclusive prefix over warps per expert slot
+  for (int e = tid; e < p.slots; e += kRouteThreads) {
+    int run = 0;
+    for (int w = 0; w < kRouteWarps; ++w) {
+      const int c = whist[w * p.slots + e];
+      whist[w * p.slots + e] = run;
+      run += c;
+    }
+    cnt[e] = run;
+    p.counts[e] = run;
+  }
+  __syncthreads();
+  // ---- 3. offsets (exclusive scan over slots) by warp 0
+  if (warp == 0) {
+    const int per = (p.slots + 31) >> 5;
+    int local = 0;
+    for (int j = 0; j < per; ++j) {
+      const int e = lane * per + j;
+      if (e < p.slots) local += cnt[e];
+    }
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    int run = incl - local;
+    for (int j = 0; j < per; ++j) {
+      const int e = lane * per + j;
+      if (e < p.slots) { offs[e] = run; run += cnt[e]; }
+    }
+    if (lane == 31) { offs[p.slots] = incl; p.counts[p.slots] = incl; }
+  }
+  __syncthreads();
+
+  // ---- 4. stable positions: offset of the expert + routes of that expert before this one
+  for (int b = 0; b < chunk; b += 32) {
+    const int i = r0 + b + lane;
+    const int e = (i < R) ? rexp[i] : -1;
+    const uint32_t m = __match_any_sync(0xffffffffu, e);
+    if (i < R) {
+      if (e >= 0) {
+        const int q = offs[e] + whist[warp * p.slots + e] + __popc(m & ((1u << lane) - 1u));
+        const int t = i / p.kk, s = i - t * p.kk;
+        float w = 1.0f;
+        if (s < p.k) w = (p.logits != nullptr) ? p.wts_out[t * p.k + s] : p.wts_in[t * p.k + s];
+        p.pos[i] = q;
+        p.sorted[q] = i;
+        p.wsorted[q] = w;
+      } else {
+        p.pos[i] = -1;
+      }
+    }
+    __syncwarp();
+    if (e >= 0 && lane == (31 - __clz(m))) whist[warp * p.slots + e] += __popc(m);
+    __syncwarp();
+  }
+
+  // ---- 5. work items: experts by load descending (ties by id), cut into runs of <= 128 rows
+  int active = 0;
+  for (int e = tid; e < p.slots; e += kRouteThreads) {
+    const int c = cnt[e];
+    if (c > 0) {
+      int rank = 0;
+      for (int o = 0; o < p.slots; ++o) {
+        const int co = cnt[o];
+        rank += (co > c || (co == c && o < e)) ? 1 : 0;
+      }
+      order[rank] = e;
+      ++active;
+    }
+  }
+  if (active) atomicAdd(&s_nact, active);
+  __syncthreads();
+  const int n_active = s_nact;
+  if (warp == 0) {
+    const int per = (n_active + 31) >> 5;
+    int local = 0;
+    for (int j = 0; j < per; ++j) {
+      const int r = lane * per + j;
+      if (r < n_active) local += (cnt[order[r]] + kChunkRows - 1) / kChunkRows;
+    }
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    int run = incl - local;
+    for (int j = 0; j < per; ++j) {
+      const int r = lane * per + j;
+      if (r < n_active) { ibase[r] = run; run += (cnt[order[r]] + kChunkRows - 1) / kChunkRows; }
+    }
+    if (lane == 31) {
+      p.meta[kMetaItems] = incl < p.max_items ? incl : p.max_items;
+      p.meta[kMetaLocalRoutes] = offs[p.slots];
+      p.meta[kMetaStatus] = 0;
+      p.meta[kMetaDetail] = 0;
+      p.meta[kMetaTokens] = p.T;
+    }
+  }
+  __syncthreads();
+  for (int r = tid; r < n_active; r += kRouteThreads) {
+    const int e = order[r];
+    const int c = cnt[e];
+    int it = ibase[r];
+    for (int c0 = 0; c0 < c && it < p.max_items; c0 += kChunkRows, ++it) {
+      const int n = min(kChunkRows, c - c0);
+      int npad = 16;
+      while (npad < n) npad <<= 1;
+      p.items[it] = make_int4(e, offs[e] + c0, n, npad);
+    }
+  }
+}
+
+// xg[pos] = hidden[token of the route at pos]: rows of the gate_up GEMM's token operand in expert order.
+__global__ void __launch_bounds__(128) okc_gather_rows(const uint16_t* __restrict__ hidden, int64_t stride,
+                                                       const int32_t* __restrict__ meta,
+                                                       const int32_t* __restrict__ sorted, int kk, int H,
+                                                       uint16_t* __restrict__ xg) {
+  const int q = blockIdx.x;
+  if (q >= meta[kMetaLocalRoutes]) return;
+  const int t = sorted[q] / kk;
+  const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * stride);
+  uint4* dst = reinterpret_cast<uint4*>(xg + static_cast<size_t>(q) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+size_t route_smem_bytes(int R, int slots) {
+  return sizeof(int32_t) * (static_cast<size_t>(R) + kRouteWarps * slots + slots + 3 * (slots + 1));
+}
+
+cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
+  const size_t smem = route_smem_bytes(p.T * p.kk, p.slots);
+  cudaError_t e = cudaFuncSetAttribute(okc_route_sort, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  okc_route_sort<<<1, kRouteThreads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather(const void* hidden, int64_t stride, const int32_t* meta, const int32_t* sorted, int kk,
+                          int H, int R, void* xg, cudaStream_t stream) {
+  okc_gather_rows<<<R, 128, 0, stream>>>(static_cast<const uint16_t*>(hidden), stride, meta, sorted, kk, H,
+                                         static_cast<uint16_t*>(xg));
+  return cudaGetLastError();
+}
+
+}  // namespace okc

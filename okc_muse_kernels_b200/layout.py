@@ -1,0 +1,175 @@
+"""The packed ("stage image") weight format the sm_100a kernels stream, stated in numpy.
+
+The repack is lossless (same number of bytes as the NVFP4 tensors it is made from: 4 bits per
+code + one E4M3 byte per 16 codes) and plays the role of the reference's prepare-time repackers
+``_pack_weight`` / ``_pack_scales`` / ``_sq_pack`` (muse_moe_w4a16/submission.py:5916-5952), for a
+different consumer: here the consumer is one thread per weight row that turns 32 codes into 16
+bf16x2 registers and stores them to tensor memory as the A operand of ``tcgen05.mma``.
+
+Geometry
+--------
+A GEMM ``D[rows, tokens] = W[rows, K] . X[tokens, K]^T`` is cut into *units*: one expert, one pair
+of 128-row tiles (gate tile + matching up tile for w13; two adjacent tiles for w2).  A unit is
+streamed as K/256 *stages*; a stage is 36 864 contiguous bytes::
+
+    [tile A image 18 432 B][tile B image 18 432 B]
+    tile image = codes  [chunk c = 0..7][row r = 0..127][16 B]      (16 384 B)
+                 scales [chunk c = 0..7][row r = 0..127][ 2 B]      ( 2 048 B)
+
+Chunk c of row r holds K elements ``k0 + 32c .. k0 + 32c + 31`` (two 16-element scale blocks): four
+32-bit words ``(w0, w1)`` for block 0 and ``(w2, w3)`` for block 1, and the blocks' two scale bytes.
+
+Bits inside a word pair
+-----------------------
+The 16 codes of a block are bit-permuted so that eight mask/rotate operations produce eight
+bf16x2 registers whose halves are ``code value * 2**-126`` (sign at bit 15, the three magnitude
+bits at bits 8:6 of each half): ``out = rotr(src, s) & 0x81C081C0``.  Six registers come straight
+from ``w0`` (rotations 0, 4, 10) and ``w1`` (rotations 2, 6, 12); the bits those leave over in both
+words are merged with one select, ``u = (w0 & LEFT) | (w1 & ~LEFT)``, and give the last two
+(rotations 8, 14).  ``PAIR_BITS[j][b]`` is the (word, bit) that holds bit ``b`` of code ``j``.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+TILE_ROWS = 128
+STAGE_K = 256
+CHUNK_K = 32
+CHUNKS = STAGE_K // CHUNK_K                      # 8
+TILE_CODE_BYTES = CHUNKS * TILE_ROWS * 16        # 16384
+TILE_SCALE_BYTES = CHUNKS * TILE_ROWS * 2        # 2048
+TILE_BYTES = TILE_CODE_BYTES + TILE_SCALE_BYTES  # 18432
+STAGE_BYTES = 2 * TILE_BYTES                     # 36864
+
+OUT_MASK = 0x81C081C0
+# (source, rotation) of the eight output registers; source 0 = w0, 1 = w1, 2 = u
+OUT_PLAN = ((0, 0), (0, 4), (0, 10), (1, 2), (1, 6), (1, 12), (2, 8), (2, 14))
+# target bit of code bit b (0 = mantissa, 1..2 = exponent, 3 = sign) in the low half of a register
+_HALF_BITS = (6, 7, 8, 15)
+
+
+def _left_mask() -> int:
+    """Bits of w0 that its three rotations do not use (the same residues mod 16 in both halves)."""
+    used = 0
+    for src, rot in OUT_PLAN:
+        if src == 0:
+            for t in range(32):
+                if (OUT_MASK >> t) & 1:
+                    used |= 1 << ((t + rot) % 32)
+    return (~used) & 0xFFFFFFFF
+
+
+LEFT_MASK = _left_mask()
+
+
+def _pair_bits():
+    table = [[None] * 4 for _ in range(16)]
+    seen = set()
+    for i, (src, rot) in enumerate(OUT_PLAN):
+        for half in range(2):
+            j = 2 * i + half
+            for b in range(4):
+                p = (_HALF_BITS[b] + 16 * half + rot) % 32
+                if src == 2:
+                    word = 0 if (LEFT_MASK >> p) & 1 else 1
+                else:
+                    word = src
+                assert (word, p) not in seen
+                seen.add((word, p))
+                table[j][b] = (word, p)
+    assert len(seen) == 64
+    return table
+
+
+PAIR_BITS = _pair_bits()
+# flat form for the CUDA repack kernel: PAIR_SHIFT[j*4+b] = word*32 + bit
+PAIR_SHIFT = [PAIR_BITS[j][b][0] * 32 + PAIR_BITS[j][b][1] for j in range(16) for b in range(4)]
+
+
+def pack_block(codes16: np.ndarray) -> np.ndarray:
+    """uint8 codes [..., 16] (one 16-element scale block) -> uint32 [..., 2] bit-permuted words."""
+    c = np.asarray(codes16, dtype=np.uint64)
+    out = np.zeros(c.shape[:-1], dtype=np.uint64)
+    for j in range(16):
+        for b in range(4):
+            out |= ((c[..., j] >> np.uint64(b)) & np.uint64(1)) << np.uint64(PAIR_SHIFT[j * 4 + b])
+    return np.stack(((out & np.uint64(0xFFFFFFFF)), (out >> np.uint64(32))), axis=-1).astype(np.uint32)
+
+
+def _rotr(x: np.ndarray, s: int) -> np.ndarray:
+    x = x.astype(np.uint32)
+    if s == 0:
+        return x
+    return ((x >> np.uint32(s)) | (x << np.uint32(32 - s))).astype(np.uint32)
+
+
+def unpack_block_regs(words: np.ndarray) -> np.ndarray:
+    """What the device does with a word pair: uint32 [..., 2] -> eight bf16x2 registers [..., 8]
+    (before the multiply by the block scale)."""
+    w0 = words[..., 0].astype(np.uint32)
+    w1 = words[..., 1].astype(np.uint32)
+    u = (w0 & np.uint32(LEFT_MASK)) | (w1 & np.uint32(~LEFT_MASK & 0xFFFFFFFF))
+    srcs = (w0, w1, u)
+    return np.stack([_rotr(srcs[s], r) & np.uint32(OUT_MASK) for s, r in OUT_PLAN], axis=-1)
+
+
+def regs_to_values(regs: np.ndarray) -> np.ndarray:
+    """bf16x2 registers [..., 8] -> float32 E2M1 values [..., 16] (undoing the 2**-126)."""
+    lo = (regs & np.uint32(0xFFFF)).astype(np.uint32) << np.uint32(16)
+    hi = (regs & np.uint32(0xFFFF0000)).astype(np.uint32)
+    both = np.stack((lo, hi), axis=-1).reshape(*regs.shape[:-1], 16)
+    return (both.view(np.float32).astype(np.float64) * 2.0 ** 126).astype(np.float32)
+
+
+def _codes(packed: np.ndarray) -> np.ndarray:
+    p = np.asarray(packed, dtype=np.uint8)
+    return np.stack((p & 0x0F, p >> 4), axis=-1).reshape(*p.shape[:-1], p.shape[-1] * 2)
+
+
+def pack_tile_stage(packed_rows: np.ndarray, sf_rows: np.ndarray) -> np.ndarray:
+    """One tile image: packed codes uint8 [128, 128] (K = 256) + scales uint8 [128, 16] -> uint8 [18432]."""
+    codes = _codes(packed_rows).reshape(TILE_ROWS, CHUNKS, 2, 16)         # row, chunk, block, code
+    words = pack_block(codes)                                              # row, chunk, block, 2
+    code_img = np.ascontiguousarray(words.transpose(1, 0, 2, 3)).view(np.uint8).reshape(-1)
+    sc = np.asarray(sf_rows, dtype=np.uint8).reshape(TILE_ROWS, CHUNKS, 2)
+    scale_img = np.ascontiguousarray(sc.transpose(1, 0, 2)).reshape(-1)
+    return np.concatenate((code_img, scale_img))
+
+
+def repack_matrix(packed: np.ndarray, sf: np.ndarray, pair_rows) -> np.ndarray:
+    """Repack one expert's matrix (packed uint8 [rows, K/2], sf uint8 [rows, K/16]).
+
+    ``pair_rows(p) -> (first row of tile A, first row of tile B)``.  Returns uint8
+    [n_pairs, K/256, 36864]."""
+    rows, kb = packed.shape
+    k = kb * 2
+    n_pairs = rows // (2 * TILE_ROWS)
+    stages = k // STAGE_K
+    out = np.empty((n_pairs, stages, STAGE_BYTES), dtype=np.uint8)
+    for p in range(n_pairs):
+        ra, rb = pair_rows(p)
+        for s in range(stages):
+            for t, r0 in enumerate((ra, rb)):
+                out[p, s, t * TILE_BYTES:(t + 1) * TILE_BYTES] = pack_tile_stage(
+                    packed[r0:r0 + TILE_ROWS, s * 128:(s + 1) * 128],
+                    sf[r0:r0 + TILE_ROWS, s * 16:(s + 1) * 16])
+    return out
+
+
+def repack_w13(packed: np.ndarray, sf: np.ndarray) -> np.ndarray:
+    """w13 of one expert ([2I, H/2], rows [0,I) gate, [I,2I) up): pair p = gate rows 128p.. with
+    up rows I + 128p.. ."""
+    inter = packed.shape[0] // 2
+    return repack_matrix(packed, sf, lambda p: (TILE_ROWS * p, inter + TILE_ROWS * p))
+
+
+def repack_w2(packed: np.ndarray, sf: np.ndarray) -> np.ndarray:
+    """w2 of one expert ([H, I/2]): pair p = rows 256p.. and 256p + 128.. ."""
+    return repack_matrix(packed, sf, lambda p: (2 * TILE_ROWS * p, 2 * TILE_ROWS * p + TILE_ROWS))
+
+
+def packed_bytes(hidden: int, inter: int) -> tuple[int, int]:
+    """Bytes of one expert's repacked w13 and w2."""
+    b13 = (inter // TILE_ROWS) * (hidden // STAGE_K) * STAGE_BYTES
+    b2 = (hidden // (2 * TILE_ROWS)) * (inter // STAGE_K) * STAGE_BYTES
+    return b13, b2

@@ -1,0 +1,272 @@
+"""Host side of the NVFP4 W4A16 MoE decode step: the reference's callable surface over the C ABI.
+
+The reference exposes ``prepare(weights) -> state`` (once, untimed) and ``kernel_fn(data, state) ->
+bf16 [M, H]`` (muse_moe_w4a16/TASK.md:24, muse_moe_w4a16/submission.py:6011, 6518) with the input
+dictionaries of submission.py:23-48.  The same two names are kept here with the same argument
+meaning, plus ``moe_step`` which also runs the router (softmax top-k) on the GPU.
+
+Every tensor operation on the hot path is one of this library's CUDA kernels, reached through
+``libokc_moe_b200.so``; PyTorch only owns the device memory and the stream.  There is no CPU path
+and no PyTorch fallback: a missing library or a non-CUDA tensor raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, replace
+
+import torch
+
+from . import _lib
+from ._lib import OkcError, Plan, Sizes
+
+__all__ = ["MoEPlan", "prepare", "kernel_fn", "moe_step", "route", "sorted_routes", "unpack_bf16", "read_status",
+           "OkcError"]
+
+
+@dataclass(frozen=True)
+class MoEPlan:
+    """Shape of one MoE layer shard (the reference's ``config`` dict, reference.py:83-84, as a type)."""
+    hidden: int
+    inter: int
+    n_experts: int
+    top_k: int
+    local_start: int = 0
+    local_count: int | None = None
+    shared_inter: int = 0
+    max_tokens: int = 256
+    post_norm: bool = False
+
+    def __post_init__(self):
+        if self.local_count is None:
+            object.__setattr__(self, "local_count", self.n_experts - self.local_start)
+
+    @classmethod
+    def from_config(cls, cfg: dict, **kw) -> "MoEPlan":
+        """From the ``config`` dict the reference puts into its inputs."""
+        return cls(hidden=cfg["d_hidden"], inter=cfg["d_expert"], n_experts=cfg["n_experts"], top_k=cfg["top_k"],
+                   local_start=cfg["local_start"], local_count=cfg["local_count"], **kw)
+
+    def c_plan(self) -> Plan:
+        p = Plan()
+        p.hidden, p.inter, p.n_experts, p.top_k = self.hidden, self.inter, self.n_experts, self.top_k
+        p.local_start, p.local_count, p.shared_inter = self.local_start, self.local_count, self.shared_inter
+        p.max_tokens, p.post_norm = self.max_tokens, int(self.post_norm)
+        return p
+
+    def sizes(self) -> Sizes:
+        s = Sizes()
+        _lib.check(_lib.lib().okc_moe_query(C.byref(self.c_plan()), C.byref(s)), "okc_moe_query")
+        return s
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("okc_muse_kernels_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def _u8(t: torch.Tensor) -> torch.Tensor:
+    return t.contiguous().view(torch.uint8)
+
+
+def prepare(weights: dict, plan: MoEPlan | None = None, *, top_k: int = 8, max_tokens: int = 256) -> dict:
+    """Lossless repack of the NVFP4 expert weights for this GPU's shard; once, untimed.
+
+    ``weights`` is the reference's dictionary (reference.py:33-50): ``w13`` uint8 [E, 2I, H/2],
+    ``w13_sf`` e4m3 [E, 2I, H/16], ``w13_gs`` f32 [E], ``w2`` uint8 [E, H, I/2], ``w2_sf`` [E, H, I/16],
+    ``w2_gs`` [E], optional ``post_norm_w`` bf16 [H] (used when ``plan.post_norm``), optional shared
+    expert ``shared_w13`` [2I, H/2], ``shared_w13_sf``, ``shared_w13_gs`` [] and the same for ``w2``.
+    The expert dimension may hold all ``n_experts`` or just the ``local_count`` local ones.
+    Returns the state dictionary ``kernel_fn`` / ``moe_step`` take; it holds tensors and the plan only,
+    so a caller may clone it (the reference's judge does, muse_moe_w4a16/bench.py:47-56).
+    """
+    w13, w2 = weights["w13"], weights["w2"]
+    _need_cuda(w13, w2)
+    if plan is None:
+        has_post = "post_norm_w" in weights
+        plan = MoEPlan(hidden=w13.shape[2] * 2, inter=w13.shape[1] // 2, n_experts=w13.shape[0], top_k=top_k,
+                       shared_inter=(weights["shared_w13"].shape[0] // 2 if "shared_w13" in weights else 0),
+                       max_tokens=max_tokens, post_norm=has_post)
+    cp = plan.c_plan()
+    sz = plan.sizes()
+    dev = w13.device
+    if w13.shape[0] == plan.n_experts:
+        sel = slice(plan.local_start, plan.local_start + plan.local_count)
+    elif w13.shape[0] == plan.local_count:
+        sel = slice(0, plan.local_count)
+    else:
+        raise ValueError("weights hold neither n_experts nor local_count experts")
+    if w13.shape[1:] != (2 * plan.inter, plan.hidden // 2) or w2.shape[1:] != (plan.hidden, plan.inter // 2):
+        raise ValueError("weight shapes do not match the plan")
+    packed13 = torch.empty(sz.packed_w13_bytes, dtype=torch.uint8, device=dev)
+    packed2 = torch.empty(sz.packed_w2_bytes, dtype=torch.uint8, device=dev)
+    lib = _lib.lib()
+    stream = _stream()
+    # repack in groups so the temporaries of the contiguous copies stay small
+    group = 16
+    for e0 in range(0, plan.local_count, group):
+        n = min(group, plan.local_count - e0)
+        s = slice(sel.start + e0, sel.start + e0 + n)
+        a, asf, b, bsf = _u8(w13[s]), _u8(weights["w13_sf"][s]), _u8(w2[s]), _u8(weights["w2_sf"][s])
+        _lib.check(lib.okc_moe_repack(C.byref(cp), a.data_ptr(), asf.data_ptr(), b.data_ptr(), bsf.data_ptr(), e0, n,
+                                      packed13.data_ptr(), packed2.data_ptr(), stream), "okc_moe_repack")
+        torch.cuda.current_stream().synchronize()   # a, asf, b, bsf may be temporaries
+    gs13 = weights["w13_gs"].to(torch.float32).reshape(-1)[sel]
+    gs2 = weights["w2_gs"].to(torch.float32).reshape(-1)[sel]
+    if plan.shared_inter:
+        a, asf = _u8(weights["shared_w13"][None]), _u8(weights["shared_w13_sf"][None])
+        b, bsf = _u8(weights["shared_w2"][None]), _u8(weights["shared_w2_sf"][None])
+        _lib.check(lib.okc_moe_repack(C.byref(cp), a.data_ptr(), asf.data_ptr(), b.data_ptr(), bsf.data_ptr(),
+                                      plan.local_count, 1, packed13.data_ptr(), packed2.data_ptr(), stream),
+                   "okc_moe_repack(shared)")
+        torch.cuda.current_stream().synchronize()
+        gs13 = torch.cat([gs13, weights["shared_w13_gs"].to(torch.float32).reshape(1)])
+        gs2 = torch.cat([gs2, weights["shared_w2_gs"].to(torch.float32).reshape(1)])
+    state = {
+        "plan": plan,
+        "packed_w13": packed13, "packed_w2": packed2,
+        "gs13": gs13.contiguous(), "gs2": gs2.contiguous(),
+        "post_norm_w": weights["post_norm_w"].to(torch.bfloat16).contiguous() if plan.post_norm else None,
+        "workspace": torch.zeros(sz.workspace_bytes, dtype=torch.uint8, device=dev),
+        "ids": torch.zeros((plan.max_tokens, plan.top_k), dtype=torch.int32, device=dev),
+        "wts": torch.zeros((plan.max_tokens, plan.top_k), dtype=torch.float32, device=dev),
+    }
+    return state
+
+
+def _check_hidden(hidden: torch.Tensor, plan: MoEPlan) -> tuple[int, int]:
+    _need_cuda(hidden)
+    if hidden.dtype != torch.bfloat16 or hidden.dim() != 2 or hidden.shape[1] != plan.hidden:
+        raise ValueError(f"hidden_states must be bf16 [T, {plan.hidden}]")
+    if hidden.shape[0] < 1 or hidden.shape[0] > plan.max_tokens:
+        raise ValueError(f"T = {hidden.shape[0]} outside 1..max_tokens = {plan.max_tokens}")
+    if hidden.stride(1) != 1 or hidden.stride(0) % 8 or hidden.data_ptr() % 16:
+        hidden = hidden.contiguous()
+    return hidden, hidden.stride(0)
+
+
+def _own(plan: MoEPlan, T: int, own_tokens) -> tuple[int, int]:
+    if not plan.shared_inter:
+        return 0, 0
+    return (0, T) if own_tokens is None else (int(own_tokens[0]), int(own_tokens[1]))
+
+
+def _experts(hidden, stride, T, state, out, out_f32):
+    plan: MoEPlan = state["plan"]
+    _lib.check(_lib.lib().okc_moe_experts(
+        C.byref(plan.c_plan()), state["packed_w13"].data_ptr(), state["packed_w2"].data_ptr(),
+        state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, T,
+        _ptr(state["post_norm_w"]), state["workspace"].data_ptr(), out.data_ptr(), int(out_f32), _stream()),
+        "okc_moe_experts")
+
+
+def kernel_fn(data: dict, state: dict, *, out_f32: bool = False, own_tokens=None) -> torch.Tensor:
+    """The reference's timed entry (submission.py:6518): routing given as ``topk_ids`` int32 [T, k]
+    (global ids; ids outside this shard, -1 included, are skipped) and ``topk_weights`` f32 [T, k].
+    Returns a new bf16 [T, H] tensor (f32 partial sums with ``out_f32``); rows with no local route
+    are zero.  Graph-capturable: no host sync, no branching on values."""
+    plan: MoEPlan = state["plan"]
+    cfg = data.get("config")
+    if cfg is not None:
+        for key, val in (("top_k", plan.top_k), ("local_start", plan.local_start), ("local_count", plan.local_count),
+                         ("d_hidden", plan.hidden), ("d_expert", plan.inter), ("n_experts", plan.n_experts)):
+            if key in cfg and cfg[key] != val:
+                raise ValueError(f"config[{key!r}] = {cfg[key]} but the state was prepared for {val}")
+    hidden, stride = _check_hidden(data["hidden_states"], plan)
+    T = hidden.shape[0]
+    ids = data["topk_ids"]
+    wts = data["topk_weights"]
+    _need_cuda(ids, wts)
+    if ids.shape != (T, plan.top_k) or wts.shape != (T, plan.top_k):
+        raise ValueError("topk_ids / topk_weights must be [T, top_k]")
+    ids = ids.to(torch.int32).contiguous()
+    wts = wts.to(torch.float32).contiguous()
+    t0, t1 = _own(plan, T, own_tokens)
+    _lib.check(_lib.lib().okc_moe_sort(C.byref(plan.c_plan()), ids.data_ptr(), wts.data_ptr(), T, t0, t1,
+                                       state["workspace"].data_ptr(), _stream()), "okc_moe_sort")
+    out = torch.empty((T, plan.hidden), dtype=torch.float32 if out_f32 else torch.bfloat16, device=hidden.device)
+    _experts(hidden, stride, T, state, out, out_f32)
+    return out
+
+
+def route(router_logits: torch.Tensor, state: dict, *, own_tokens=None):
+    """Softmax top-k routing + the token->expert sort into the state's workspace.  Returns views of
+    the state's ``ids`` int32 [T, k] and ``wts`` f32 [T, k] buffers."""
+    plan: MoEPlan = state["plan"]
+    _need_cuda(router_logits)
+    if router_logits.dtype != torch.float32 or router_logits.dim() != 2 or router_logits.shape[1] != plan.n_experts:
+        raise ValueError(f"router_logits must be f32 [T, {plan.n_experts}]")
+    T = router_logits.shape[0]
+    if T < 1 or T > plan.max_tokens:
+        raise ValueError(f"T = {T} outside 1..max_tokens = {plan.max_tokens}")
+    router_logits = router_logits.contiguous()
+    t0, t1 = _own(plan, T, own_tokens)
+    _lib.check(_lib.lib().okc_moe_route(C.byref(plan.c_plan()), router_logits.data_ptr(), T, t0, t1,
+                                        state["ids"].data_ptr(), state["wts"].data_ptr(),
+                                        state["workspace"].data_ptr(), _stream()), "okc_moe_route")
+    return state["ids"][:T], state["wts"][:T]
+
+
+def moe_step(hidden_states: torch.Tensor, router_logits: torch.Tensor, state: dict, *, out_f32: bool = False,
+             own_tokens=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One MoE decode step: bf16 hidden [T, H] + f32 router logits [T, E] -> bf16 [T, H].
+
+    Router: softmax over the experts, top-k (ties to the lowest index), weights renormalised over
+    the selected; experts: SiLU(gate)*up, FP32 accumulation; rows are the routing-weighted sum of
+    this shard's experts (+ the shared expert for ``own_tokens``).  ``out_f32`` returns the FP32
+    partial sum an expert-parallel reduce-scatter consumes."""
+    plan: MoEPlan = state["plan"]
+    hidden, stride = _check_hidden(hidden_states, plan)
+    T = hidden.shape[0]
+    if router_logits.shape[0] != T:
+        raise ValueError("hidden_states and router_logits disagree on T")
+    route(router_logits, state, own_tokens=own_tokens)
+    if out is None:
+        out = torch.empty((T, plan.hidden), dtype=torch.float32 if out_f32 else torch.bfloat16, device=hidden.device)
+    _experts(hidden, stride, T, state, out, out_f32)
+    return out
+
+
+def sorted_routes(state: dict, T: int, max_items: int | None = None) -> dict:
+    """The sort tables of the last route / kernel_fn call, copied out for inspection."""
+    plan: MoEPlan = state["plan"]
+    sz = plan.sizes()
+    dev = state["workspace"].device
+    R = T * sz.routes_per_token
+    max_items = max_items or (sz.expert_slots + R // 128 + 1)
+    counts = torch.empty(sz.expert_slots, dtype=torch.int32, device=dev)
+    srt = torch.empty(R, dtype=torch.int32, device=dev)
+    pos = torch.empty(R, dtype=torch.int32, device=dev)
+    items = torch.zeros(1 + 4 * max_items, dtype=torch.int32, device=dev)
+    _lib.check(_lib.lib().okc_moe_export_sort(C.byref(plan.c_plan()), state["workspace"].data_ptr(), T,
+                                              counts.data_ptr(), srt.data_ptr(), pos.data_ptr(), items.data_ptr(),
+                                              max_items, _stream()), "okc_moe_export_sort")
+    n = int(items[0])
+    return {"counts": counts, "sorted": srt, "pos": pos, "items": items[1:1 + 4 * n].view(n, 4)}
+
+
+def unpack_bf16(state: dict, which: int, slot: int) -> torch.Tensor:
+    """Dequantises one repacked matrix on the GPU: bf16 [rows, K] = code * block scale * 2**-8."""
+    plan: MoEPlan = state["plan"]
+    rows, k = (2 * plan.inter, plan.hidden) if which == 0 else (plan.hidden, plan.inter)
+    packed = state["packed_w13"] if which == 0 else state["packed_w2"]
+    out = torch.empty((rows, k), dtype=torch.bfloat16, device=packed.device)
+    _lib.check(_lib.lib().okc_moe_unpack_bf16(C.byref(plan.c_plan()), packed.data_ptr(), which, slot,
+                                              out.data_ptr(), _stream()), "okc_moe_unpack_bf16")
+    return out
+
+
+def read_status(state: dict) -> tuple[int, int]:
+    """(status, detail) of the last step: (0, 0), or (OKC_ERR_TIMEOUT, code of the wait that ran out).
+    Synchronises the current stream."""
+    detail = C.c_int32(0)
+    rc = _lib.lib().okc_moe_read_status(state["workspace"].data_ptr(), _stream(), C.byref(detail))
+    return rc, detail.value

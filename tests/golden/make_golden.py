@@ -4,7 +4,7 @@ modules (muse_moe_w4a16/{nvfp4,reference,checks}.py) on the CPU.
     python tests/golden/make_golden.py /path/to/reference
 
 The reference hard-codes its shapes as module constants (reference.py:18-22); they are patched to
-small sizes here so the fixtures stay a few hundred KB.  Nothing in the test-suite needs the
+small sizes here (the narrowest the CUDA kernels accept: multiples of 256) so the fixtures stay small.  Nothing in the test-suite needs the
 reference tree at run time: the tests only read the .npz files this script wrote.
 """
 from __future__ import annotations
@@ -121,13 +121,13 @@ def main() -> None:
 
     cases = {}
     # the reference's own weight distribution (uniform codes, log-normal scales), with post-norm, all local
-    cases.update(moe_vectors(ref, nvfp4, "full", hidden=256, inter=128, experts=8, top_k=2, local=(0, 8),
+    cases.update(moe_vectors(ref, nvfp4, "full", hidden=256, inter=256, experts=4, top_k=2, local=(0, 4),
                              bs=5, seed=1000, dist="normal", quantised_normal=False))
     # expert-parallel shard (4 of 8 local, busiest-rank rotation), skewed routing + outlier channels
-    cases.update(moe_vectors(ref, nvfp4, "ep", hidden=128, inter=128, experts=8, top_k=3, local=(0, 4),
+    cases.update(moe_vectors(ref, nvfp4, "ep", hidden=256, inter=256, experts=4, top_k=3, local=(0, 2),
                              bs=7, seed=1003, dist="skewed", quantised_normal=False))
     # N(0,0.02) weights through the reference's quantiser (the distribution the benchmark configs use)
-    cases.update(moe_vectors(ref, nvfp4, "qn", hidden=256, inter=128, experts=4, top_k=2, local=(0, 4),
+    cases.update(moe_vectors(ref, nvfp4, "qn", hidden=256, inter=256, experts=2, top_k=2, local=(0, 2),
                              bs=4, seed=1001, dist="normal", quantised_normal=True))
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **cases)
 

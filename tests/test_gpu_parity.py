@@ -1,0 +1,334 @@
+"""GPU parity tests (run with -m gpu on a B200): every check goes through the C ABI
+(okc_muse_kernels_b200 -> libokc_moe_b200.so) and compares with the numpy oracle on the same
+seeded inputs.  Tolerances: routing ids / sort tables / repack bytes bit-exact; routing weights to
+float32 round-off; layer output max-abs-err <= 2e-2 and rel-L2 <= 1e-2 against the
+FP32-accumulated oracle (the bound stated for this path), plus the reference's own checker
+(rel-L2 <= 1.5e-2, rows <= 7.5e-2; muse_moe_w4a16/checks.py:31-55)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import okc_muse_kernels_b200 as okc
+from okc_muse_kernels_b200 import layout, synth
+from oracle import moe_np, nvfp4_np as fp4
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2
+REL_L2 = 1e-2
+
+
+def _dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _bits(t: torch.Tensor) -> np.ndarray:
+    return t.detach().cpu().contiguous().view(torch.uint16).numpy()
+
+
+def _check_out(out: torch.Tensor, ref_f32: np.ndarray, what: str):
+    got = moe_np.bf16_to_f32(_bits(out)).astype(np.float64)
+    ref = ref_f32.astype(np.float64)
+    assert np.isfinite(got).all(), what
+    max_abs = np.abs(got - ref).max()
+    rel = np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-12)
+    assert max_abs <= MAX_ABS and rel <= REL_L2, f"{what}: max-abs {max_abs:.3e} rel-L2 {rel:.3e}"
+    ok, msg = moe_np.compare(_bits(out), ref_f32, 1.5e-2)
+    assert ok, f"{what}: {msg}"
+    return max_abs, rel
+
+
+def _status_ok(state):
+    rc, detail = okc.read_status(state)
+    assert rc == 0, f"device status {rc} detail {detail:#x}"
+
+
+SMALL = synth.Workload("small", 5, 512, 256, 8, 2)
+
+
+@pytest.fixture(scope="module")
+def small():
+    dev = _dev()
+    w = synth.make_weights(SMALL, seed=11, device=dev)
+    plan = okc.MoEPlan(hidden=SMALL.hidden, inter=SMALL.inter, n_experts=SMALL.n_experts, top_k=SMALL.top_k,
+                       max_tokens=64)
+    return w, synth.to_numpy_weights(w), okc.prepare(w, plan)
+
+
+def test_repack_bytes_match_layout(small):
+    w, wn, state = small
+    b13, b2 = layout.packed_bytes(SMALL.hidden, SMALL.inter)
+    p13 = state["packed_w13"].cpu().numpy().reshape(SMALL.n_experts, b13)
+    p2 = state["packed_w2"].cpu().numpy().reshape(SMALL.n_experts, b2)
+    for e in (0, 3, 7):
+        assert np.array_equal(p13[e], layout.repack_w13(wn["w13"][e], wn["w13_sf"][e]).reshape(-1))
+        assert np.array_equal(p2[e], layout.repack_w2(wn["w2"][e], wn["w2_sf"][e]).reshape(-1))
+
+
+def test_device_dequant_is_exact(small):
+    w, wn, state = small
+    for which, key in ((0, "w13"), (1, "w2")):
+        for e in (0, 5):
+            got = moe_np.bf16_to_f32(_bits(okc.unpack_bf16(state, which, e)))
+            ref = fp4.dequantize(wn[key][e], wn[f"{key}_sf"][e], 1.0) * np.float32(2.0 ** -8)
+            assert np.array_equal(got, ref), f"{key}[{e}]"
+
+
+def test_device_dequant_all_scale_bytes_and_codes():
+    """Every non-negative finite E4M3 scale byte (zero and subnormals included) times every code."""
+    dev = _dev()
+    wl = synth.Workload("t", 1, 256, 256, 1, 1)
+    rng = np.random.default_rng(0)
+    w13 = rng.integers(0, 256, (1, 512, 128)).astype(np.uint8)
+    w13_sf = (np.arange(512 * 16).reshape(1, 512, 16) % 0x7F).astype(np.uint8)
+    w2 = rng.integers(0, 256, (1, 256, 128)).astype(np.uint8)
+    w2_sf = rng.integers(0, 0x7F, (1, 256, 16)).astype(np.uint8)
+    weights = {"w13": torch.from_numpy(w13).to(dev), "w13_sf": torch.from_numpy(w13_sf).to(dev),
+               "w13_gs": torch.ones(1, device=dev), "w2": torch.from_numpy(w2).to(dev),
+               "w2_sf": torch.from_numpy(w2_sf).to(dev), "w2_gs": torch.ones(1, device=dev)}
+    state = okc.prepare(weights, okc.MoEPlan(hidden=256, inter=256, n_experts=1, top_k=1, max_tokens=4))
+    got = moe_np.bf16_to_f32(_bits(okc.unpack_bf16(state, 0, 0)))
+    ref = fp4.dequantize(w13[0], w13_sf[0], 1.0) * np.float32(2.0 ** -8)
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))       # bit-exact, signed zeros too
+
+
+@pytest.mark.parametrize("T,E,k", [(4, 16, 2), (32, 128, 8), (1, 128, 8), (33, 128, 8), (128, 256, 8), (512, 160, 6)])
+def test_route_ids_bit_exact(T, E, k):
+    dev = _dev()
+    g = torch.Generator(device="cpu").manual_seed(100 + T)
+    logits = torch.randn((T, E), generator=g)
+    if T > 3:
+        logits[1, 5] = logits[1, 9] = logits[1].max() + 1      # tie for first place
+        logits[2, :] = 0.5                                      # all equal
+        logits[3, 7] = float("-inf")
+    plan = okc.MoEPlan(hidden=256, inter=256, n_experts=E, top_k=k, max_tokens=max(T, 16))
+    sz = plan.sizes()
+    state = {"plan": plan, "workspace": torch.zeros(sz.workspace_bytes, dtype=torch.uint8, device=dev),
+             "ids": torch.zeros((plan.max_tokens, k), dtype=torch.int32, device=dev),
+             "wts": torch.zeros((plan.max_tokens, k), dtype=torch.float32, device=dev)}
+    ids, wts = okc.route(logits.to(dev), state)
+    ref_ids, ref_w = moe_np.route_softmax_topk(logits.numpy(), k)
+    assert np.array_equal(ids.cpu().numpy(), ref_ids)
+    assert np.allclose(wts.cpu().numpy(), ref_w, rtol=2e-6, atol=1e-9)
+    # the sort tables, bit-exact against the oracle's stable sort
+    s = okc.sorted_routes(state, T)
+    ref = moe_np.sort_routes(ref_ids, 0, E)
+    assert np.array_equal(s["counts"].cpu().numpy(), ref["counts"])
+    n = len(ref["sorted"])
+    assert np.array_equal(s["sorted"].cpu().numpy()[:n], ref["sorted"])
+    assert np.all(s["sorted"].cpu().numpy()[n:] == -1)
+    assert np.array_equal(s["pos"].cpu().numpy(), ref["pos"])
+    assert np.array_equal(s["items"].cpu().numpy()[:, :3], ref["items"])
+
+
+def test_sort_with_local_range_and_foreign_ids():
+    dev = _dev()
+    rng = np.random.default_rng(7)
+    T, E, k = 40, 64, 4
+    ids = rng.integers(0, E, (T, k)).astype(np.int32)
+    ids[0, :] = -1                       # the value the reference's layer passes for off-GPU slots
+    ids[1, :] = 20                       # the same expert twice in one token
+    ids[2, :] = 63
+    wts = rng.random((T, k)).astype(np.float32)
+    plan = okc.MoEPlan(hidden=256, inter=256, n_experts=E, top_k=k, local_start=16, local_count=16, max_tokens=64)
+    sz = plan.sizes()
+    state = {"plan": plan, "workspace": torch.zeros(sz.workspace_bytes, dtype=torch.uint8, device=dev)}
+    from okc_muse_kernels_b200 import _lib
+    import ctypes as C
+    i_d, w_d = torch.from_numpy(ids).to(dev), torch.from_numpy(wts).to(dev)
+    _lib.check(_lib.lib().okc_moe_sort(C.byref(plan.c_plan()), i_d.data_ptr(), w_d.data_ptr(), T, 0, 0,
+                                       state["workspace"].data_ptr(), torch.cuda.current_stream().cuda_stream), "sort")
+    s = okc.sorted_routes(state, T)
+    ref = moe_np.sort_routes(ids, 16, 16)
+    assert np.array_equal(s["counts"].cpu().numpy(), ref["counts"])
+    assert np.array_equal(s["pos"].cpu().numpy(), ref["pos"])
+    assert np.array_equal(s["items"].cpu().numpy()[:, :3], ref["items"])
+
+
+@pytest.mark.parametrize("T", [1, 5, 33])
+def test_small_step_matches_oracle(small, T):
+    w, wn, state = small
+    hidden, logits = synth.make_inputs(SMALL, seed=500 + T, device=_dev(), tokens=T)
+    out = okc.moe_step(hidden, logits, state)
+    _status_ok(state)
+    assert out.shape == (T, SMALL.hidden) and out.dtype == torch.bfloat16
+    _, ref, ids, _ = moe_np.moe_step(_bits(hidden), logits.cpu().numpy(), wn, SMALL.top_k)
+    assert np.array_equal(state["ids"][:T].cpu().numpy(), ids)
+    _check_out(out, ref, f"small T={T}")
+
+
+def test_config1_matches_oracle():
+    wl = synth.WORKLOADS["c1"]
+    dev = _dev()
+    w = synth.make_weights(wl, device=dev)
+    state = okc.prepare(w, okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=wl.n_experts, top_k=wl.top_k,
+                                       max_tokens=16))
+    hidden, logits = synth.make_inputs(wl, seed=1001, device=dev)
+    out = okc.moe_step(hidden, logits, state)
+    _status_ok(state)
+    _, ref, ids, _ = moe_np.moe_step(_bits(hidden), logits.cpu().numpy(), synth.to_numpy_weights(w), wl.top_k)
+    assert np.array_equal(state["ids"][:wl.tokens].cpu().numpy(), ids)
+    _check_out(out, ref, "config 1")
+    # determinism: a second call gives the same bits
+    out2 = okc.moe_step(hidden, logits, state)
+    assert torch.equal(out, out2)
+
+
+def test_kernel_fn_post_norm_and_local_range_against_oracle():
+    """Reference semantics (given ids/weights, post-expert RMSNorm, a local expert range, tokens
+    without a local route -> exact zeros, a cloned state) at a shape the kernels accept."""
+    dev = _dev()
+    wl = synth.Workload("pn", 9, 512, 256, 16, 4)
+    w = synth.make_weights(wl, seed=21, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    w["post_norm_w"] = (0.1 * torch.randn((wl.hidden,), generator=g)).to(torch.bfloat16).to(dev)
+    plan = okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=16, top_k=4, local_start=4, local_count=8,
+                       max_tokens=32, post_norm=True)
+    state = okc.prepare(w, plan)
+    state = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in state.items()}   # cloned state
+    hidden, logits = synth.make_inputs(wl, seed=77, device=dev)
+    ids, wts = moe_np.route_softmax_topk(logits.cpu().numpy(), 4)
+    ids[0, :] = [0, 1, 2, 3]            # token 0 has no local route
+    ids[1, :] = [5, 5, 6, 15]           # the same expert twice
+    data = {"hidden_states": hidden, "topk_ids": torch.from_numpy(ids).to(dev),
+            "topk_weights": torch.from_numpy(wts).to(dev),
+            "config": {"bs": wl.tokens, "d_hidden": wl.hidden, "d_expert": wl.inter, "n_experts": 16,
+                       "local_start": 4, "local_count": 8, "top_k": 4, "sharding": "ep"}}
+    out = okc.kernel_fn(data, state)
+    _status_ok(state)
+    wn = synth.to_numpy_weights(w)
+    ref = moe_np.experts(_bits(hidden), ids, wts, wn, local_start=4, local_count=8)
+    assert not out[0].any(), "a token with no local route must be exact zeros"
+    _check_out(out, ref, "post-norm + local range")
+    # non-contiguous hidden states (a column slice of a wider tensor)
+    wide = torch.zeros((wl.tokens, wl.hidden + 64), dtype=torch.bfloat16, device=dev)
+    wide[:, :wl.hidden] = hidden
+    data["hidden_states"] = wide[:, :wl.hidden]
+    out2 = okc.kernel_fn(data, state)
+    assert torch.equal(out, out2)
+
+
+def test_shared_expert_and_f32_partials_sum_like_expert_parallel_ranks():
+    """Two shards of one layer on one GPU: partial sums (FP32) add up to the full answer, the
+    shared expert only on each shard's own token block."""
+    dev = _dev()
+    wl = synth.Workload("sh", 8, 512, 256, 8, 2, shared_inter=256)
+    w = synth.make_weights(wl, seed=31, device=dev)
+    hidden, logits = synth.make_inputs(wl, seed=9, device=dev)
+    wn = synth.to_numpy_weights(w)
+    shared = {k[len("shared_"):]: v for k, v in wn.items() if k.startswith("shared_")}
+    _, ref, partials = moe_np.moe_step_ep(_bits(hidden), logits.cpu().numpy(), wn, 2, 2, shared)
+    acc = torch.zeros((wl.tokens, wl.hidden), dtype=torch.float32, device=dev)
+    for r in range(2):
+        plan = okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=8, top_k=2, local_start=4 * r, local_count=4,
+                           shared_inter=256, max_tokens=16)
+        st = okc.prepare(w, plan)
+        part = okc.moe_step(hidden, logits, st, out_f32=True, own_tokens=(4 * r, 4 * r + 4))
+        _status_ok(st)
+        p = part.cpu().numpy()
+        rel = np.linalg.norm(p - partials[r]) / np.linalg.norm(partials[r])
+        assert rel < 5e-3, f"rank {r} partial rel-L2 {rel:.3e}"
+        acc += part
+    _check_out(acc.to(torch.bfloat16), ref, "sum of shard partials")
+
+
+def test_config2_parity_and_properties():
+    """Config 2 (T=32, H=4096, I=1536, E=128, top-8) against the oracle on a subset of tokens, and
+    size-independent properties on the whole output."""
+    wl = synth.WORKLOADS["c2"]
+    dev = _dev()
+    w = synth.make_weights(wl, device=dev)
+    state = okc.prepare(w, okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=wl.n_experts, top_k=wl.top_k,
+                                       max_tokens=256))
+    hidden, logits = synth.make_inputs(wl, seed=1002, device=dev)
+    out = okc.moe_step(hidden, logits, state)
+    _status_ok(state)
+    wn = synth.to_numpy_weights(w)
+    sub = [0, 13, 31]
+    _, ref, ids, _ = moe_np.moe_step(_bits(hidden)[sub], logits.cpu().numpy()[sub], wn, wl.top_k)
+    assert np.array_equal(state["ids"][:32].cpu().numpy()[sub], ids)
+    _check_out(out[sub], ref, "config 2 (token subset)")
+    # a token's row does not depend on which other tokens share the batch
+    out_sub = okc.moe_step(hidden[sub].contiguous(), logits[sub].contiguous(), state)
+    assert torch.equal(out_sub, out[sub])
+    # run-to-run determinism
+    assert torch.equal(out, okc.moe_step(hidden, logits, state))
+    # scaling the hidden states by 2 (exact in bf16) scales gate and up: out(2x) != 2 out(x), but
+    # zero hidden states give exact zeros
+    z = okc.moe_step(torch.zeros_like(hidden), logits, state)
+    assert not z.any()
+
+
+@pytest.mark.parametrize("T", [2, 64, 128, 256])
+def test_batch_sweep_rows_match_config2_single_rows(T):
+    """Config 3: every token's output at batch T equals its output computed alone (token counts per
+    expert from 1 to > 16 exercise every padded width of the token operand)."""
+    wl = synth.WORKLOADS["c2"]
+    dev = _dev()
+    w = synth.make_weights(wl, device=dev, n_experts=16)
+    wl16 = synth.Workload("c3", T, wl.hidden, wl.inter, 16, 8)
+    state = okc.prepare(w, okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=16, top_k=8, max_tokens=256))
+    hidden, logits = synth.make_inputs(wl16, seed=1003, device=dev)
+    out = okc.moe_step(hidden, logits, state)
+    _status_ok(state)
+    for t in (0, T // 2, T - 1):
+        one = okc.moe_step(hidden[t:t + 1].contiguous(), logits[t:t + 1].contiguous(), state)
+        assert torch.equal(one[0], out[t]), f"token {t} of {T}"
+    wn = synth.to_numpy_weights(w)
+    sub = [0, T - 1]
+    _, ref, _, _ = moe_np.moe_step(_bits(hidden)[sub], logits.cpu().numpy()[sub], wn, 8)
+    _check_out(out[sub], ref, f"batch {T}")
+
+
+def test_zipf_routing_hot_expert_chunks():
+    """Config 5's routing skew at a narrower width: one expert takes > 128 tokens, so its rows are cut
+    into several work items."""
+    dev = _dev()
+    wl = synth.Workload("z", 300, 512, 256, 40, 6, zipf_alpha=1.2)
+    w = synth.make_weights(wl, seed=41, device=dev)
+    state = okc.prepare(w, okc.MoEPlan(hidden=512, inter=256, n_experts=40, top_k=6, max_tokens=512))
+    hidden, logits = synth.make_inputs(wl, seed=42, device=dev)
+    out = okc.moe_step(hidden, logits, state)
+    _status_ok(state)
+    s = okc.sorted_routes(state, 300)
+    assert int(s["counts"].max()) > 128
+    _, ref, ids, _ = moe_np.moe_step(_bits(hidden), logits.cpu().numpy(), synth.to_numpy_weights(w), 6)
+    assert np.array_equal(state["ids"][:300].cpu().numpy(), ids)
+    _check_out(out, ref, "zipf")
+
+
+def _golden(tag):
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "moe.npz"))
+    return {k[len(tag) + 1:]: g[k] for k in g.files if k.startswith(tag + "_")}
+
+
+@pytest.mark.parametrize("tag", ["full", "ep", "qn"])
+def test_kernel_fn_matches_reference_golden_vectors(tag):
+    """Against outputs of the reference's own ref_kernel (tests/golden/moe.npz): given routing,
+    post-expert norm, a local expert range; checked with the reference's acceptance test and the
+    tighter bound of this path."""
+    g = _golden(tag)
+    bs, hidden, inter, experts, top_k, lo, cnt = (int(v) for v in g["cfg"])
+    dev = _dev()
+    weights = {"w13": torch.from_numpy(g["w13"]).to(dev), "w13_sf": torch.from_numpy(g["w13_sf"]).to(dev),
+               "w13_gs": torch.from_numpy(g["w13_gs"]).to(dev), "w2": torch.from_numpy(g["w2"]).to(dev),
+               "w2_sf": torch.from_numpy(g["w2_sf"]).to(dev), "w2_gs": torch.from_numpy(g["w2_gs"]).to(dev),
+               "post_norm_w": torch.from_numpy(g["post_norm_w"].view(np.int16)).view(torch.bfloat16).to(dev)}
+    plan = okc.MoEPlan(hidden=hidden, inter=inter, n_experts=experts, top_k=top_k, local_start=lo, local_count=cnt,
+                       max_tokens=16, post_norm=True)
+    state = okc.prepare(weights, plan)
+    data = {"hidden_states": torch.from_numpy(g["hidden"].view(np.int16)).view(torch.bfloat16).to(dev),
+            "topk_ids": torch.from_numpy(g["ids"]).to(dev), "topk_weights": torch.from_numpy(g["wts"]).to(dev),
+            "config": {"bs": bs, "d_hidden": hidden, "d_expert": inter, "n_experts": experts, "local_start": lo,
+                       "local_count": cnt, "top_k": top_k, "sharding": "case"}}
+    out = okc.kernel_fn(data, state)
+    _status_ok(state)
+    ref = moe_np.bf16_to_f32(g["out"])
+    ok, msg = moe_np.compare(_bits(out), ref, 1.5e-2)
+    assert ok, msg
+    got = moe_np.bf16_to_f32(_bits(out)).astype(np.float64)
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= REL_L2, f"{tag}: rel-L2 {rel:.3e}"

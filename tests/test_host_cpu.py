@@ -1,0 +1,155 @@
+"""CPU-side checks: the C-ABI library loads and exports every declared symbol, plan validation,
+the packed layout's bit permutation, the synthetic-data quantiser against the oracle, and the
+oracle's routing / sort helpers."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from okc_muse_kernels_b200 import _lib, layout, synth
+from okc_muse_kernels_b200.moe import MoEPlan
+from oracle import moe_np, nvfp4_np as fp4
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "okc_moe.h")).read()
+    declared = set(re.findall(r"\b(okc_moe_[a-z0-9_]+)\s*\(", header))
+    declared -= {"okc_moe_plan", "okc_moe_sizes", "okc_moe_error"}
+    assert declared, "no declarations found"
+    handle = C.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(handle, name), f"{name} declared in include/okc_moe.h but not exported"
+    assert declared == set(_lib.SIGNATURES), "ctypes table and header disagree"
+    assert _lib.lib().okc_moe_version() >= 100
+
+
+def test_query_and_plan_validation():
+    plan = MoEPlan(hidden=4096, inter=1536, n_experts=128, top_k=8, max_tokens=32)
+    sz = plan.sizes()
+    b13, b2 = layout.packed_bytes(4096, 1536)
+    assert sz.packed_w13_bytes == 128 * b13 and sz.packed_w2_bytes == 128 * b2
+    # lossless: same bytes as the NVFP4 tensors (4 bits per code + 1 byte per 16 codes)
+    assert b13 == 2 * 1536 * 4096 * 9 // 16 and b2 == 4096 * 1536 * 9 // 16
+    assert sz.expert_slots == 128 and sz.routes_per_token == 8 and sz.workspace_bytes > 0
+    for bad in (dict(hidden=4000), dict(inter=100), dict(top_k=0), dict(n_experts=1024), dict(max_tokens=0),
+                dict(shared_inter=512), dict(local_start=120, local_count=16)):
+        kw = dict(hidden=4096, inter=1536, n_experts=128, top_k=8, max_tokens=32)
+        kw.update(bad)
+        s = _lib.Sizes()
+        rc = _lib.lib().okc_moe_query(C.byref(MoEPlan(**kw).c_plan()), C.byref(s))
+        assert rc == _lib.OKC_ERR_BAD_PLAN, bad
+    assert b"wait" in _lib.lib().okc_moe_strerror(_lib.OKC_ERR_TIMEOUT)
+
+
+def test_null_and_range_arguments_are_rejected_before_any_launch():
+    plan = MoEPlan(hidden=1024, inter=512, n_experts=16, top_k=2, max_tokens=8)
+    lib = _lib.lib()
+    cp = plan.c_plan()
+    assert lib.okc_moe_route(C.byref(cp), None, 4, 0, 0, None, None, None, None) == _lib.OKC_ERR_BAD_ARG
+    assert lib.okc_moe_sort(C.byref(cp), None, None, 4, 0, 0, None, None) == _lib.OKC_ERR_BAD_ARG
+    assert lib.okc_moe_experts(C.byref(cp), None, None, None, None, None, 1024, 4, None, None, None, 0, None) \
+        == _lib.OKC_ERR_BAD_ARG
+    assert lib.okc_moe_repack(C.byref(cp), None, None, None, None, 0, 1, None, None, None) == _lib.OKC_ERR_BAD_ARG
+    assert lib.okc_moe_read_status(None, None, None) == _lib.OKC_ERR_BAD_ARG
+
+
+def test_bit_permutation_round_trip():
+    rng = np.random.default_rng(1)
+    codes = rng.integers(0, 16, (4096, 16)).astype(np.uint8)
+    vals = layout.regs_to_values(layout.unpack_block_regs(layout.pack_block(codes)))
+    expect = np.where(codes & 8, -fp4.E2M1_GRID[codes & 7], fp4.E2M1_GRID[codes & 7])
+    assert np.array_equal(vals, expect)
+    assert np.array_equal(np.signbit(vals), (codes & 8) != 0)   # -0 stays -0: lossless
+    assert len(set(layout.PAIR_SHIFT)) == 64
+
+
+def test_cuda_bit_table_matches_layout_module():
+    src = open(os.path.join(ROOT, "okc_muse_kernels_b200", "csrc", "repack.cu")).read()
+    body = src[src.index("kPairShift[64] = {") + len("kPairShift[64] = {"):]
+    nums = [int(x) for x in re.findall(r"\d+", body[:body.index("}")])]
+    assert nums == layout.PAIR_SHIFT
+    fmt = open(os.path.join(ROOT, "okc_muse_kernels_b200", "csrc", "format.cuh")).read()
+    assert f"0x{layout.LEFT_MASK:08X}u" in fmt and f"0x{layout.OUT_MASK:08X}u" in fmt
+
+
+def test_tile_image_layout():
+    rng = np.random.default_rng(2)
+    packed = rng.integers(0, 256, (128, 128)).astype(np.uint8)
+    sf = rng.integers(0, 0x7F, (128, 16)).astype(np.uint8)
+    img = layout.pack_tile_stage(packed, sf)
+    assert img.shape == (layout.TILE_BYTES,)
+    row, chunk = 37, 5
+    words = img[:layout.TILE_CODE_BYTES].view(np.uint32).reshape(8, 128, 4)[chunk, row]
+    vals = layout.regs_to_values(layout.unpack_block_regs(words.reshape(2, 2))).reshape(32)
+    assert np.array_equal(vals, fp4.unpack_e2m1(packed[row, chunk * 16:(chunk + 1) * 16]))
+    sc = img[layout.TILE_CODE_BYTES:].reshape(8, 128, 2)[chunk, row]
+    assert np.array_equal(sc, sf[row, 2 * chunk:2 * chunk + 2])
+
+
+def test_torch_quantiser_matches_oracle_bit_exact():
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn((64, 256), generator=g) * 0.02
+    x[0, :16] = 0
+    x[1, 3] = 0.5
+    p, sf, gs = synth.quantize_nvfp4(x)
+    p2, sf2, gs2 = fp4.quantize(x.numpy())
+    assert np.float32(gs.item()).view(np.uint32) == np.float32(gs2).view(np.uint32)
+    assert np.array_equal(sf.view(torch.uint8).numpy(), sf2)
+    assert np.array_equal(p.numpy(), p2)
+
+
+def test_softmax_topk_oracle_properties():
+    rng = np.random.default_rng(4)
+    logits = rng.standard_normal((33, 128)).astype(np.float32)
+    logits[3, 10] = logits[3, 90] = logits[3].max() + 1.0       # a tie for first place
+    logits[5, :] = 0.25                                          # everything ties
+    ids, w = moe_np.route_softmax_topk(logits, 8)
+    assert ids[3, 0] == 10 and ids[3, 1] == 90
+    assert np.array_equal(ids[5], np.arange(8))
+    assert np.allclose(w.sum(axis=1), 1.0, atol=1e-6)
+    # equals softmax over all experts, top-k, renormalised over the selected (tie-free rows)
+    sm = np.exp(logits - logits.max(axis=1, keepdims=True))
+    sm /= sm.sum(axis=1, keepdims=True)
+    for t in (0, 1, 2, 7, 20):
+        top = np.argsort(-sm[t], kind="stable")[:8]
+        assert np.array_equal(top, ids[t])
+        assert np.allclose(sm[t, top] / sm[t, top].sum(), w[t], rtol=1e-5)
+
+
+def test_sort_oracle_is_stable_and_chunks_items():
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, 16, (300, 4)).astype(np.int32)
+    ids[:, 0] = 3                                              # one hot expert: 300 rows -> 3 items
+    s = moe_np.sort_routes(ids, local_start=2, local_count=8, chunk=128)
+    assert s["counts"].sum() == ((ids >= 2) & (ids < 10)).sum()
+    flat = ids.reshape(-1)
+    srt = s["sorted"]
+    ex = flat[srt] - 2
+    assert np.all(np.diff(ex) >= 0)
+    for e in range(8):
+        r = srt[ex == e]
+        assert np.all(np.diff(r) > 0)                          # route-index order inside an expert
+    assert np.array_equal(s["pos"][srt], np.arange(len(srt)))
+    assert np.all(s["pos"][(flat < 2) | (flat >= 10)] == -1)
+    items = s["items"]
+    hot = 300 + int((ids[:, 1:] == 3).sum())                   # expert 3 is local slot 1
+    n_hot = -(-hot // 128)
+    assert np.all(items[:n_hot, 0] == 1)
+    assert list(items[:n_hot, 2]) == [128] * (n_hot - 1) + [hot - 128 * (n_hot - 1)]
+    assert list(items[:n_hot, 1]) == [int(s["offsets"][1]) + 128 * i for i in range(n_hot)]
+    loads = [s["counts"][e] for e in items[:, 0]]
+    assert all(loads[i] >= loads[i + 1] for i in range(len(loads) - 1))
+
+
+def test_workload_table_matches_baseline_configs():
+    w = synth.WORKLOADS
+    assert (w["c1"].tokens, w["c1"].hidden, w["c1"].inter, w["c1"].n_experts, w["c1"].top_k) == (4, 1024, 512, 16, 2)
+    assert (w["c2"].tokens, w["c2"].hidden, w["c2"].inter, w["c2"].n_experts, w["c2"].top_k) == (32, 4096, 1536, 128, 8)
+    assert (w["c4"].hidden, w["c4"].inter, w["c4"].n_experts, w["c4"].shared_inter) == (7168, 2048, 256, 2048)
+    assert (w["c5"].tokens, w["c5"].n_experts, w["c5"].top_k, w["c5"].zipf_alpha) == (512, 160, 6, 1.2)
+    assert synth.algorithmic_bytes(w["c2"], 1, 0) == 10616832      # 10.617 MB per touched expert
