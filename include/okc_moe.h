@@ -111,6 +111,20 @@ int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void
                     int T, const void* post_norm_w, void* workspace, void* out, int out_f32,
                     okc_stream_t stream);
 
+/* okc_moe_experts with CUDA events around its four kernels: synchronises, then writes their
+ * durations in milliseconds to the host array phase_ms[4] = {gather, gate_up, down, combine}.
+ * A measurement aid (it creates and destroys five events); not for the serving path.  Plays the
+ * role of the reference's DIAG timing harness (submission.py:6151-6231). */
+int okc_moe_experts_profiled(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                             const float* gs13, const float* gs2, const void* hidden,
+                             int64_t hidden_stride, int T, const void* post_norm_w, void* workspace,
+                             void* out, int out_f32, okc_stream_t stream, float* phase_ms);
+
+/* f32 [n] -> bf16 [n] (n % 4 == 0): the cast after an expert-parallel reduce-scatter of FP32
+ * partial sums.  The reference has no counterpart (its expert all-reduce is not run,
+ * muse_moe_w4a16/baseline.py:8). */
+int okc_moe_cast_bf16(const float* in, void* out_bf16, int64_t n, okc_stream_t stream);
+
 /* okc_moe_route followed by okc_moe_experts. */
 int okc_moe_step(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
                  const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,

@@ -45,6 +45,9 @@ SIGNATURES = {
     "okc_moe_route": (C.c_int, [_PLAN, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
     "okc_moe_sort": (C.c_int, [_PLAN, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "okc_moe_experts": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P]),
+    "okc_moe_experts_profiled": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P,
+                                           C.POINTER(C.c_float)]),
+    "okc_moe_cast_bf16": (C.c_int, [_P, _P, C.c_int64, _P]),
     "okc_moe_step": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P,
                                _P, C.c_int, _P]),
     "okc_moe_export_sort": (C.c_int, [_PLAN, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P]),

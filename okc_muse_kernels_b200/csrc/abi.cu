@@ -193,10 +193,11 @@ int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weig
                       reinterpret_cast<cudaStream_t>(stream));
 }
 
-int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
-                    const float* gs2, const void* hidden, int64_t hidden_stride, int T, const void* post_norm_w,
-                    void* workspace, void* out, int out_f32, okc_stream_t stream_) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+// Launches the four kernels of the expert phase; `ev`, when given, holds five events recorded
+// before / between / after them (gather, gate_up, down, combine).
+static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
+                        const float* gs2, const void* hidden, int64_t hidden_stride, int T, const void* post_norm_w,
+                        void* workspace, void* out, int out_f32, cudaStream_t stream, cudaEvent_t* ev) {
   Geometry g;
   if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
   if (!packed_w13 || !packed_w2 || !gs13 || !gs2 || !hidden || !workspace || !out) return OKC_ERR_BAD_ARG;
@@ -213,7 +214,9 @@ int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void
   const int R = T * g.kk;
   const int ncap = ncap_for(T);
 
+  if (ev && cudaEventRecord(ev[0], stream) != cudaSuccess) return OKC_ERR_CUDA;
   if (launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (ev && cudaEventRecord(ev[1], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
   GemmParams a;
   memset(&a, 0, sizeof(a));
@@ -225,6 +228,7 @@ int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void
   a.ncap = ncap; a.n_stages = gemm_stages_for(ncap);
   a.inter = w.inter; a.I = g.I; a.H = g.H;
   if (launch_gemm(0, a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (ev && cudaEventRecord(ev[2], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
   GemmParams b;
   memset(&b, 0, sizeof(b));
@@ -236,12 +240,49 @@ int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void
   b.y = w.y; b.sorted = w.sorted; b.wsorted = w.wsorted; b.H = g.H; b.I = g.I;
   b.weighted = plan->post_norm ? 0 : 1;
   if (launch_gemm(1, b, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (ev && cudaEventRecord(ev[3], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
   CombineParams c;
   c.y = w.y; c.pos = w.pos; c.wsorted = w.wsorted; c.post_w = static_cast<const uint16_t*>(post_norm_w);
   c.out = out; c.kk = g.kk; c.H = g.H; c.out_f32 = out_f32 ? 1 : 0;
   if (launch_combine(c, T, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (ev && cudaEventRecord(ev[4], stream) != cudaSuccess) return OKC_ERR_CUDA;
   return OKC_OK;
+}
+
+int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
+                    const float* gs2, const void* hidden, int64_t hidden_stride, int T, const void* post_norm_w,
+                    void* workspace, void* out, int out_f32, okc_stream_t stream) {
+  return experts_impl(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, T, post_norm_w, workspace, out,
+                      out_f32, reinterpret_cast<cudaStream_t>(stream), nullptr);
+}
+
+int okc_moe_experts_profiled(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                             const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride, int T,
+                             const void* post_norm_w, void* workspace, void* out, int out_f32, okc_stream_t stream_,
+                             float* phase_ms) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!phase_ms) return OKC_ERR_BAD_ARG;
+  cudaEvent_t ev[5];
+  int made = 0;
+  int rc = OKC_OK;
+  for (; made < 5; ++made)
+    if (cudaEventCreate(&ev[made]) != cudaSuccess) { rc = OKC_ERR_CUDA; break; }
+  if (rc == OKC_OK)
+    rc = experts_impl(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, T, post_norm_w, workspace, out,
+                      out_f32, stream, ev);
+  if (rc == OKC_OK && cudaEventSynchronize(ev[4]) != cudaSuccess) rc = OKC_ERR_CUDA;
+  if (rc == OKC_OK)
+    for (int i = 0; i < 4; ++i)
+      if (cudaEventElapsedTime(&phase_ms[i], ev[i], ev[i + 1]) != cudaSuccess) rc = OKC_ERR_CUDA;
+  for (int i = 0; i < made; ++i) cudaEventDestroy(ev[i]);
+  return rc;
+}
+
+int okc_moe_cast_bf16(const float* in, void* out_bf16, int64_t n, okc_stream_t stream) {
+  if (!in || !out_bf16 || n < 0 || (n % 4) != 0 || !aligned(in, 16) || !aligned(out_bf16, 8)) return OKC_ERR_BAD_ARG;
+  if (n == 0) return OKC_OK;
+  return launch_cast(in, out_bf16, n, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
 }
 
 int okc_moe_step(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,

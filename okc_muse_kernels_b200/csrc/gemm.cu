@@ -357,6 +357,27 @@ __global__ void __launch_bounds__(kCombineThreads) okc_combine(const CombinePara
   }
 }
 
+// f32 -> bf16 (round to nearest even), four elements per thread: the last step of the
+// expert-parallel path, after the reduce-scatter of the FP32 partial sums.
+__global__ void __launch_bounds__(256) okc_cast_bf16(const float4* __restrict__ in, uint2* __restrict__ out, int64_t nvec) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const float4 a = in[i];
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(a.z, a.w);
+  uint2 o;
+  o.x = *reinterpret_cast<const uint32_t*>(&lo);
+  o.y = *reinterpret_cast<const uint32_t*>(&hi);
+  out[i] = o;
+}
+
+cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t stream) {
+  const int64_t nvec = n / 4;
+  okc_cast_bf16<<<static_cast<unsigned>((nvec + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const float4*>(in), static_cast<uint2*>(out_bf16), nvec);
+  return cudaGetLastError();
+}
+
 size_t gemm_smem_bytes(int n_stages, int ncap) {
   return 1024 + static_cast<size_t>(n_stages) * (kStageBytes + static_cast<size_t>(ncap) * 512) + sizeof(Ctrl);
 }

@@ -69,6 +69,7 @@ struct CombineParams {
 };
 cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream);
 
+cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t stream);
 size_t route_smem_bytes(int R, int slots);
 size_t gemm_smem_bytes(int n_stages, int ncap);
 

@@ -1,0 +1,105 @@
+"""Expert-parallel MoE step over the GPUs of one box: one process per GPU, NCCL over NVLink.
+
+Sharding follows the reference's expert-parallel semantics (muse_moe_w4a16/reference.py:22,98-101:
+a GPU computes only the routes whose expert id lies in its contiguous local range, and the layer
+output is the sum of the GPUs' partial results); the reference never runs that sum ("the expert
+all-reduce is not run", muse_moe_w4a16/baseline.py:8), so the exchange steps here are new:
+
+    1. all-gather of the ranks' token blocks: hidden bf16 [T/world, H] and router logits f32 [T/world, E]
+    2. every rank routes all T tokens identically and runs its local experts on them, plus the
+       replicated shared expert on its own token block only -> FP32 partial sums [T, H]
+    3. reduce-scatter of the partial sums (FP32, so the cross-GPU sum adds no bf16 rounding)
+    4. cast of the rank's own rows to bf16
+
+Rank r holds experts [r*E/world, (r+1)*E/world) and owns token rows [r*T/world, (r+1)*T/world).
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+from .moe import MoEPlan, cast_bf16, moe_step, prepare
+
+
+def shard_plan(hidden: int, inter: int, n_experts: int, top_k: int, world: int, rank: int, max_tokens: int,
+               shared_inter: int = 0) -> MoEPlan:
+    """The plan of rank `rank`'s shard: experts cut contiguously, E/world per rank."""
+    if n_experts % world:
+        raise ValueError(f"{n_experts} experts do not divide over {world} ranks")
+    per = n_experts // world
+    return MoEPlan(hidden=hidden, inter=inter, n_experts=n_experts, top_k=top_k, local_start=rank * per,
+                   local_count=per, shared_inter=shared_inter, max_tokens=max_tokens)
+
+
+def token_block(tokens: int, world: int, rank: int) -> tuple[int, int]:
+    if tokens % world:
+        raise ValueError(f"{tokens} tokens do not divide over {world} ranks")
+    tb = tokens // world
+    return rank * tb, (rank + 1) * tb
+
+
+def _reduce_scatter_rows(own: torch.Tensor, full: torch.Tensor, group) -> None:
+    """own[tb, H] = sum over ranks of full[rank block].  NCCL has the collective; gloo (the CPU
+    test harness) does not, there the sum is an all-reduce followed by a slice."""
+    if dist.get_backend(group) == "nccl":
+        dist.reduce_scatter_tensor(own, full, group=group)
+    else:
+        dist.all_reduce(full, group=group)
+        r = dist.get_rank(group)
+        own.copy_(full[r * own.shape[0]:(r + 1) * own.shape[0]])
+
+
+class ExpertParallelMoE:
+    """One rank's end of the expert-parallel step.
+
+    ``local_step(hidden_all, logits_all, own_tokens, out_f32)`` computes the rank's FP32 partial sums;
+    by default it is this library's CUDA step on the state prepared from ``weights`` (the rank's
+    local experts, or the whole layer from which the local range is taken).  A test harness may
+    inject ``local_step`` and ``cast`` (both or neither) to exercise the sharding and the collectives
+    on CPU ranks; nothing in this module computes on the CPU by itself.
+    """
+
+    def __init__(self, plan: MoEPlan, tokens: int, weights: dict | None = None, group=None,
+                 local_step: Callable | None = None, cast: Callable | None = None,
+                 device: torch.device | str | None = None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.plan = plan
+        self.tokens = tokens
+        self.own = token_block(tokens, self.world, self.rank)
+        tb = tokens // self.world
+        if local_step is None:
+            if weights is None:
+                raise ValueError("weights are required for the CUDA path")
+            self.state = prepare(weights, plan)
+            device = self.state["workspace"].device
+            self._local_step = self._cuda_step
+            self._cast = cast_bf16
+        else:
+            if cast is None:
+                raise ValueError("a harness that injects local_step must inject cast too")
+            self.state = None
+            self._local_step = local_step
+            self._cast = cast
+            device = torch.device(device or "cpu")
+        self.hidden_all = torch.empty((tokens, plan.hidden), dtype=torch.bfloat16, device=device)
+        self.logits_all = torch.empty((tokens, plan.n_experts), dtype=torch.float32, device=device)
+        self.partial = torch.empty((tokens, plan.hidden), dtype=torch.float32, device=device)
+        self.own_f32 = torch.empty((tb, plan.hidden), dtype=torch.float32, device=device)
+        self.out = torch.empty((tb, plan.hidden), dtype=torch.bfloat16, device=device)
+
+    def _cuda_step(self, hidden_all, logits_all, own_tokens, out_f32):
+        return moe_step(hidden_all, logits_all, self.state, out_f32=True, own_tokens=own_tokens, out=out_f32)
+
+    def step(self, hidden_own: torch.Tensor, logits_own: torch.Tensor) -> torch.Tensor:
+        """hidden_own bf16 [T/world, H], logits_own f32 [T/world, E] -> bf16 [T/world, H] (this rank's rows
+        of the layer output).  The returned tensor is reused by the next call."""
+        dist.all_gather_into_tensor(self.hidden_all, hidden_own.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(self.logits_all, logits_own.contiguous(), group=self.group)
+        self._local_step(self.hidden_all, self.logits_all, self.own, self.partial)
+        _reduce_scatter_rows(self.own_f32, self.partial, self.group)
+        self._cast(self.own_f32, self.out)
+        return self.out

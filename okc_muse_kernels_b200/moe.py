@@ -20,7 +20,7 @@ from . import _lib
 from ._lib import OkcError, Plan, Sizes
 
 __all__ = ["MoEPlan", "prepare", "kernel_fn", "moe_step", "route", "sorted_routes", "unpack_bf16", "read_status",
-           "OkcError"]
+           "experts_profiled", "cast_bf16", "OkcError"]
 
 
 @dataclass(frozen=True)
@@ -232,6 +232,31 @@ def moe_step(hidden_states: torch.Tensor, router_logits: torch.Tensor, state: di
     if out is None:
         out = torch.empty((T, plan.hidden), dtype=torch.float32 if out_f32 else torch.bfloat16, device=hidden.device)
     _experts(hidden, stride, T, state, out, out_f32)
+    return out
+
+
+def experts_profiled(hidden_states: torch.Tensor, state: dict, out: torch.Tensor) -> dict:
+    """The expert phase of a step whose routes are already sorted into the state (``route`` was
+    called), with CUDA events around its four kernels.  Synchronises; returns their durations in
+    milliseconds.  A measurement aid, not the serving path."""
+    plan: MoEPlan = state["plan"]
+    hidden, stride = _check_hidden(hidden_states, plan)
+    ms = (C.c_float * 4)()
+    _lib.check(_lib.lib().okc_moe_experts_profiled(
+        C.byref(plan.c_plan()), state["packed_w13"].data_ptr(), state["packed_w2"].data_ptr(),
+        state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, hidden.shape[0],
+        _ptr(state["post_norm_w"]), state["workspace"].data_ptr(), out.data_ptr(),
+        int(out.dtype == torch.float32), _stream(), ms), "okc_moe_experts_profiled")
+    return {"gather": ms[0], "gate_up": ms[1], "down": ms[2], "combine": ms[3]}
+
+
+def cast_bf16(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """f32 -> bf16 with this library's kernel (the tail of the expert-parallel path)."""
+    _need_cuda(x)
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.lib().okc_moe_cast_bf16(x.data_ptr(), out.data_ptr(), x.numel(), _stream()), "okc_moe_cast_bf16")
     return out
 
 

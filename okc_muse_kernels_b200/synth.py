@@ -53,10 +53,16 @@ def quantize_nvfp4(x: torch.Tensor):
     return code[..., 0] | (code[..., 1] << 4), sf, gs
 
 
-def make_weights(w: Workload, seed: int = 5252, device: str | torch.device = "cuda", n_experts: int | None = None) -> dict:
+def _expert_generator(seed: int, expert: int, device) -> torch.Generator:
+    return torch.Generator(device=device).manual_seed(seed * 1000003 + expert)
+
+
+def make_weights(w: Workload, seed: int = 5252, device: str | torch.device = "cuda", n_experts: int | None = None,
+                 first_expert: int = 0) -> dict:
     """Per expert W13 ~ N(0, 0.02) [2I, H] and W2 ~ N(0, 0.02) [H, I], quantised to NVFP4 with a
-    dynamic global scale per expert tensor (+ the shared expert when the workload has one)."""
-    g = torch.Generator(device=device).manual_seed(seed)
+    dynamic global scale per expert tensor (+ the shared expert when the workload has one).
+    Every expert has its own seed, so a shard [first_expert, first_expert + n_experts) holds the
+    same bits as the matching slice of the full layer."""
     n = w.n_experts if n_experts is None else n_experts
     out = {"w13": torch.empty((n, 2 * w.inter, w.hidden // 2), dtype=torch.uint8, device=device),
            "w13_sf": torch.empty((n, 2 * w.inter, w.hidden // 16), dtype=torch.float8_e4m3fn, device=device),
@@ -64,12 +70,14 @@ def make_weights(w: Workload, seed: int = 5252, device: str | torch.device = "cu
            "w2": torch.empty((n, w.hidden, w.inter // 2), dtype=torch.uint8, device=device),
            "w2_sf": torch.empty((n, w.hidden, w.inter // 16), dtype=torch.float8_e4m3fn, device=device),
            "w2_gs": torch.empty((n,), dtype=torch.float32, device=device)}
-    for e in range(n):
+    for i in range(n):
+        g = _expert_generator(seed, first_expert + i, device)
         a = torch.randn((2 * w.inter, w.hidden), generator=g, device=device) * 0.02
-        out["w13"][e], out["w13_sf"][e], out["w13_gs"][e] = quantize_nvfp4(a)
+        out["w13"][i], out["w13_sf"][i], out["w13_gs"][i] = quantize_nvfp4(a)
         b = torch.randn((w.hidden, w.inter), generator=g, device=device) * 0.02
-        out["w2"][e], out["w2_sf"][e], out["w2_gs"][e] = quantize_nvfp4(b)
+        out["w2"][i], out["w2_sf"][i], out["w2_gs"][i] = quantize_nvfp4(b)
     if w.shared_inter:
+        g = _expert_generator(seed, 1 << 20, device)
         a = torch.randn((2 * w.shared_inter, w.hidden), generator=g, device=device) * 0.02
         out["shared_w13"], out["shared_w13_sf"], out["shared_w13_gs"] = quantize_nvfp4(a)
         b = torch.randn((w.hidden, w.shared_inter), generator=g, device=device) * 0.02

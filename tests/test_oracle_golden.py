@@ -106,3 +106,30 @@ def test_bf16_roundtrip():
     ref = torch.from_numpy(x).to(torch.bfloat16).view(torch.uint16).numpy()
     assert np.array_equal(moe_np.f32_to_bf16(x), ref)
     assert np.array_equal(moe_np.bf16_to_f32(ref), torch.from_numpy(x).to(torch.bfloat16).float().numpy())
+
+
+@pytest.mark.parametrize("tag", ["full", "ep", "qn"])
+def test_torch_oracle_matches_ref_kernel(moe, tag):
+    """The torch-operator restatement used for the timed CPU baseline, against the same vectors."""
+    import torch
+    from oracle import moe_torch
+    bs, hidden, inter, experts, top_k, lo, cnt = (int(v) for v in moe[f"{tag}_cfg"])
+    w = {k: torch.from_numpy(moe[f"{tag}_{k}"]) for k in ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs")}
+    hid = torch.from_numpy(moe[f"{tag}_hidden"].view(np.int16)).view(torch.bfloat16)
+    post = torch.from_numpy(moe[f"{tag}_post_norm_w"].view(np.int16)).view(torch.bfloat16)
+    acc = moe_torch.experts(hid, torch.from_numpy(moe[f"{tag}_ids"]).long(), torch.from_numpy(moe[f"{tag}_wts"]), w,
+                            local_start=lo, local_count=cnt, post_norm_w=post)
+    ref = torch.from_numpy(moe[f"{tag}_out"].view(np.int16)).view(torch.bfloat16)
+    assert torch.equal(acc.to(torch.bfloat16), ref)          # same operators, same order: bit-exact
+
+
+def test_torch_and_numpy_oracles_agree_on_routing():
+    import torch
+    from oracle import moe_torch
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn((40, 128), generator=g)
+    logits[3, 7] = logits[3, 99] = 9.0
+    ids_t, w_t = moe_torch.route_softmax_topk(logits, 8)
+    ids_n, w_n = moe_np.route_softmax_topk(logits.numpy(), 8)
+    assert np.array_equal(ids_t.numpy(), ids_n)
+    assert np.allclose(w_t.numpy(), w_n, rtol=1e-6)
