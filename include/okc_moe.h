@@ -132,6 +132,34 @@ int okc_moe_step(const okc_moe_plan* plan, const void* packed_w13, const void* p
                  int32_t* ids, float* weights, void* workspace, void* out, int out_f32,
                  okc_stream_t stream);
 
+/*
+ * okc_moe_step for callers that cannot give it a workspace because they cannot allocate one.
+ * (No counterpart in the reference: its kernel_fn allocates its scratch with torch.empty on
+ * every call.)  Think of a serving process that claimed all device memory for its own pool at
+ * start-up, a plugin living inside such a process, or any caller for which cudaMalloc is off
+ * limits while it runs.  The scratch of the step is a fixed array of
+ * OKC_MOE_STATIC_SCRATCH_BYTES built into the library; each GPU that loads the library holds it
+ * until the process ends.  The call allocates nothing and frees nothing.
+ *
+ *  - Limit: the plan's workspace_bytes (okc_moe_query; it grows with max_tokens) must not exceed
+ *    OKC_MOE_STATIC_SCRATCH_BYTES, otherwise OKC_ERR_TOO_LARGE is returned and nothing runs.
+ *    Configuration 2 (H=4096, I=1536, top-8) fits up to max_tokens = 128.
+ *  - The first call on each device looks up the array's device address (the device must be
+ *    current).  Make that first call before starting any stream capture.
+ *  - All calls on a device share the one array.  The call clears the few control words that must
+ *    start at zero; everything else is overwritten by the step.  Two calls whose kernels overlap
+ *    on the GPU (different streams, or a graph replay racing a direct call) corrupt each other:
+ *    keep them on one stream or otherwise serialised.
+ *  - The status word of this variant lives in the array, so okc_moe_read_status cannot reach it.
+ * All other arguments are those of okc_moe_step.
+ */
+#define OKC_MOE_STATIC_SCRATCH_BYTES (32u << 20)
+int okc_moe_step_static_scratch(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                                const float* gs13, const float* gs2, const void* hidden,
+                                int64_t hidden_stride, const float* logits, int T, int own_t0, int own_t1,
+                                const void* post_norm_w, int32_t* ids, float* weights, void* out,
+                                int out_f32, okc_stream_t stream);
+
 /* Copies the sorted-route tables out of `workspace` for inspection (host or device pointers are
  * NOT interchangeable: all four are device pointers; any may be NULL).  counts: int32
  * [expert_slots]; sorted: int32 [T*routes_per_token] (route index t*routes_per_token+slot per

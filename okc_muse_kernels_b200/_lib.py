@@ -50,6 +50,8 @@ SIGNATURES = {
     "okc_moe_cast_bf16": (C.c_int, [_P, _P, C.c_int64, _P]),
     "okc_moe_step": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P,
                                _P, C.c_int, _P]),
+    "okc_moe_step_static_scratch": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, _P, C.c_int, C.c_int, C.c_int, _P, _P,
+                                              _P, _P, C.c_int, _P]),
     "okc_moe_export_sort": (C.c_int, [_PLAN, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P]),
     "okc_moe_unpack_bf16": (C.c_int, [_PLAN, _P, C.c_int, C.c_int, _P, _P]),
     "okc_moe_read_status": (C.c_int, [_P, _P, C.POINTER(C.c_int32)]),

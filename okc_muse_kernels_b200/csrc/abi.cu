@@ -327,4 +327,53 @@ int okc_moe_read_status(const void* workspace, okc_stream_t stream_, int32_t* de
   return host[0];
 }
 
+// ---------------------------------------------------------------------------------------------
+// A step that needs no workspace from the caller.
+//
+// Some hosts of this library may not allocate device memory at all once they are running: an
+// inference server that hands every byte of HBM to its own pool at start-up, a plugin loaded into
+// such a server, or code that runs inside a region where cudaMalloc is forbidden or would
+// synchronise the device.  For them the step's scratch (the sorted-route tables, the gathered token
+// rows, the intermediate activations and the per-route outputs) lives in an array that is part of
+// the library image itself.  Every GPU that loads the library carries these 32 MiB until the
+// process exits, whether or not this entry point is ever called.
+static __device__ __align__(256) unsigned char g_static_scratch[OKC_MOE_STATIC_SCRATCH_BYTES];
+
+// The array's name is only a host-side handle here; the device address has to be asked for, once
+// per device, while that device is current.
+constexpr int kMaxDevices = 64;
+static std::atomic<void*> g_static_scratch_ptr[kMaxDevices];
+
+static int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return OKC_ERR_CUDA;
+  if (dev < 0 || dev >= kMaxDevices) return OKC_ERR_TOO_LARGE;
+  void* p = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return OKC_ERR_CUDA;
+    g_static_scratch_ptr[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return OKC_OK;
+}
+
+int okc_moe_step_static_scratch(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                                const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,
+                                const float* logits, int T, int own_t0, int own_t1, const void* post_norm_w,
+                                int32_t* ids, float* weights, void* out, int out_f32, okc_stream_t stream) {
+  Geometry g;
+  if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  // the plan's workspace (sized by max_tokens) has to fit the array
+  if (g.total > static_cast<size_t>(OKC_MOE_STATIC_SCRATCH_BYTES)) return OKC_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != OKC_OK) return rc;
+  // The array keeps whatever the previous call left.  Only the control words at its start must
+  // read zero before the step; every table behind them is rewritten by the step itself.
+  if (cudaMemsetAsync(scratch, 0, kMetaWords * sizeof(int32_t), reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return OKC_ERR_CUDA;
+  return okc_moe_step(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, logits, T, own_t0, own_t1,
+                      post_norm_w, ids, weights, scratch, out, out_f32, stream);
+}
+
 }  // extern "C"
