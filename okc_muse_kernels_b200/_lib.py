@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libokc_moe_b200.so")
+# OKC_MOE_LIB selects another build of the same ABI (the instrumented libokc_moe_b200_prof.so)
+LIB_PATH = os.environ.get("OKC_MOE_LIB") or os.path.join(_PKG, "libokc_moe_b200.so")
 
 OKC_OK = 0
 OKC_ERR_BAD_PLAN = -1

@@ -47,9 +47,17 @@ def _compile(src: str) -> tuple[str, str]:
     return obj, r.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles and links the library; returns its path."""
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, wait_profile: bool = False) -> str:
+    """Compiles and links the library; returns its path.  ``wait_profile`` builds the instrumented
+    variant libokc_moe_b200_prof.so (-DOKC_WAIT_PROFILE: per-role wait cycles, read back with
+    okc_moe_debug_wait_profile); load it by pointing OKC_MOE_LIB at it."""
+    global OBJ
+    lib_path = LIB
+    if wait_profile:
+        lib_path = LIB.replace(".so", "_prof.so")
+        OBJ = os.path.join(PKG, "build", "prof")
+        NVCC_FLAGS.append("-DOKC_WAIT_PROFILE")
+    elif not force and not _stale():
         return LIB
     os.makedirs(OBJ, exist_ok=True)
     with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
@@ -59,12 +67,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         f.write(log)
     if verbose:
         print(log)
-    cmd = [nvcc(), "-shared", "-o", LIB, *[r[0] for r in results], "-cudart", "static"]
+    cmd = [nvcc(), "-shared", "-o", lib_path, *[r[0] for r in results], "-cudart", "static"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, wait_profile="--wait-profile" in sys.argv))

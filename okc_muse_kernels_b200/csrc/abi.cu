@@ -41,6 +41,13 @@ static bool encode_rows_map(CUtensorMap* map, void* base, uint64_t rows, uint64_
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+#ifdef OKC_WAIT_PROFILE
+static std::atomic<int> g_dbg_flags{0};
+#define OKC_DBG_FLAGS g_dbg_flags.load()
+#else
+#define OKC_DBG_FLAGS 0
+#endif
+
 static int ncap_for(int T) {
   int n = 16;
   while (n < T && n < kChunkRows) n <<= 1;
@@ -114,6 +121,12 @@ using namespace okc;
 extern "C" {
 
 int okc_moe_version(void) { return 100; }
+
+#ifdef OKC_WAIT_PROFILE
+// Experiment switches of the instrumented build: bit 0 skip the dequantisation arithmetic, bit 1 skip
+// the MMAs, bit 2 skip the tensor-memory stores.  Results are wrong with any of them set.
+int okc_moe_debug_set_flags(int flags) { g_dbg_flags.store(flags); return 0; }
+#endif
 
 const char* okc_moe_strerror(int code) {
   switch (code) {
@@ -226,7 +239,7 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   a.wpacked = static_cast<const uint8_t*>(packed_w13); a.gs = gs13; a.meta = w.meta; a.items = w.items;
   a.pairs = g.pairs13; a.stages = g.stages13; a.expert_bytes = g.w13_expert_bytes;
   a.ncap = ncap; a.n_stages = gemm_stages_for(ncap);
-  a.inter = w.inter; a.I = g.I; a.H = g.H;
+  a.inter = w.inter; a.I = g.I; a.H = g.H; a.y = w.y; a.dbg = OKC_DBG_FLAGS;
   if (launch_gemm(0, a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
   if (ev && cudaEventRecord(ev[2], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
@@ -238,7 +251,7 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   b.pairs = g.pairs2; b.stages = g.stages2; b.expert_bytes = g.w2_expert_bytes;
   b.ncap = ncap; b.n_stages = gemm_stages_for(ncap);
   b.y = w.y; b.sorted = w.sorted; b.wsorted = w.wsorted; b.H = g.H; b.I = g.I;
-  b.weighted = plan->post_norm ? 0 : 1;
+  b.weighted = plan->post_norm ? 0 : 1; b.dbg = OKC_DBG_FLAGS;
   if (launch_gemm(1, b, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
   if (ev && cudaEventRecord(ev[3], stream) != cudaSuccess) return OKC_ERR_CUDA;
 

@@ -9,9 +9,12 @@
 // One persistent CTA per SM, 24 warps:
 //   warp 0        producer: one bulk copy of the 36 KB FP4 stage image + 2-D TMA tiles of the
 //                 token operand (128-byte swizzle) per stage, mbarrier ring
-//   warp 1        MMA issuer (one thread) and owner of the TMEM allocation
-//   warps 4..19   dequantisers: thread = one weight row; FP4 + E4M3 from shared memory ->
-//                 bf16x2 registers -> tcgen05.st into a 4-slot ring of A operands in TMEM
+//   warps 1, 2    MMA issuers (one thread each: first / second tile of the pair, so every
+//                 accumulator has one issuer and a fixed order of additions); warp 1 owns the
+//                 TMEM allocation
+//   warps 4..19   dequantisers in two groups of 8 that take alternate A slots: thread = one weight
+//                 row of one tile; FP4 + E4M3 from shared memory -> bf16x2 registers -> tcgen05.st
+//                 into the 4-slot ring of A operands in TMEM (slot = one 64-wide K block)
 //   warps 20..23  epilogue: tcgen05.ld of the accumulators, scale, activation, store
 //
 // The reference computes the same products with mma.sync / wgmma on Hopper
@@ -28,6 +31,7 @@ constexpr int kGemmThreads = 768;
 constexpr int kDequantWarp0 = 4;
 constexpr int kDequantWarps = 16;
 constexpr int kEpilogueWarp0 = 20;
+constexpr int kIssuers = 2;           // MMA-issuing threads (one per tile of the pair)
 constexpr int kASlots = 4;            // ring of A operands in TMEM, 64 columns each (K = 64, two tiles)
 constexpr int kASlotCols = 64;
 constexpr int kAccCol0 = 256;         // accumulators live in TMEM columns [256, 512)
@@ -38,6 +42,26 @@ constexpr int kMaxStages = 6;
 enum WaitCode { kWaitProducerEmpty = 0x11, kWaitMmaAccEmpty = 0x21, kWaitMmaFull = 0x22, kWaitMmaAFull = 0x23,
                 kWaitDqFull = 0x31, kWaitDqAEmpty = 0x32, kWaitEpiAccFull = 0x41 };
 
+
+// Optional wait profile (compile with -DOKC_WAIT_PROFILE): per CTA, cycles each role spent in
+// each kind of wait, kept in a device array and read back by okc_moe_debug_wait_profile.  The
+// role the reference's TWM_TL timeline plays (muse_moe_w4a16/submission.py:2657-2659).
+#ifdef OKC_WAIT_PROFILE
+constexpr int kProfCtas = 256;
+constexpr int kProfSlots = 16;
+__device__ long long g_wait_prof[2][kProfCtas][kProfSlots];
+#define OKC_PROF_DECL long long prof_acc[kProfSlots] = {0}; const long long prof_t0 = clock64();
+#define OKC_PROF_WAIT(idx, expr) ([&] { const long long _t = clock64(); const bool _r = (expr); prof_acc[idx] += clock64() - _t; return _r; }())
+#define OKC_PROF_VOID(idx, stmt) { const long long _t = clock64(); stmt; prof_acc[idx] += clock64() - _t; }
+#define OKC_DBG(bit) ((p.dbg >> (bit)) & 1)
+#define OKC_PROF_STORE(idx_total, lo, hi) { prof_acc[idx_total] = clock64() - prof_t0; if (blockIdx.x < kProfCtas) for (int _i = lo; _i <= hi; ++_i) g_wait_prof[MODE][blockIdx.x][_i] = prof_acc[_i]; }
+#else
+#define OKC_DBG(bit) 0
+#define OKC_PROF_DECL
+#define OKC_PROF_WAIT(idx, expr) (expr)
+#define OKC_PROF_VOID(idx, stmt) { stmt; }
+#define OKC_PROF_STORE(idx_total, lo, hi)
+#endif
 
 struct Ctrl {
   uint64_t full[kMaxStages];
@@ -62,19 +86,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int NS = p.n_stages;
   const int nbuf = (p.ncap <= 64) ? 2 : 1;
+  // shared-memory addresses of the barrier arrays (element i is 8 bytes further)
+  const uint32_t bar_full = smem_u32(&ctrl->full[0]), bar_empty = smem_u32(&ctrl->empty[0]);
+  const uint32_t bar_afull = smem_u32(&ctrl->a_full[0]), bar_aempty = smem_u32(&ctrl->a_empty[0]);
+  const uint32_t bar_accfull = smem_u32(&ctrl->acc_full[0]), bar_accempty = smem_u32(&ctrl->acc_empty[0]);
 
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
-      mbar_init(smem_u32(&ctrl->full[i]), 1);
-      mbar_init(smem_u32(&ctrl->empty[i]), kDequantWarps + 1);
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, kDequantWarps + kIssuers);
     }
     for (int i = 0; i < kASlots; ++i) {
-      mbar_init(smem_u32(&ctrl->a_full[i]), kDequantWarps);
-      mbar_init(smem_u32(&ctrl->a_empty[i]), 1);
+      mbar_init(bar_afull + 8 * i, kDequantWarps / 2);
+      mbar_init(bar_aempty + 8 * i, kIssuers);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[i]), 4);
+      mbar_init(bar_accfull + 8 * i, kIssuers);
+      mbar_init(bar_accempty + 8 * i, 4);
     }
     ctrl->abort_code = 0;
     mbar_fence_init();
@@ -96,8 +124,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     if (lane == 0) {
       for (int i = 0; i < 4; ++i) tma_prefetch_desc(&p.bmap[i]);
       const uint64_t pol = policy_evict_first();
-      int it = 0;
+      int st = 0;
+      uint32_t ph = 0;
+      int issued = 0;
       bool ok = true;
+      OKC_PROF_DECL
       for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
         const int item = u / p.pairs, pair = u - item * p.pairs;
         const int4 wi = p.items[item];
@@ -105,109 +136,149 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         const int mi = (npad == 16) ? 0 : (npad == 32) ? 1 : (npad == 64) ? 2 : 3;
         const uint8_t* src = p.wpacked + static_cast<size_t>(wi.x) * p.expert_bytes +
                              static_cast<size_t>(pair) * p.stages * kStageBytes;
-        for (int s = 0; s < p.stages; ++s, ++it) {
-          const int st = it % NS;
-          if (!mbar_wait(smem_u32(&ctrl->empty[st]), ((it / NS) & 1) ^ 1, abort_flag, kWaitProducerEmpty)) { ok = false; break; }
-          const uint32_t bar = smem_u32(&ctrl->full[st]);
+        for (int s = 0; s < p.stages; ++s) {
+          if (!OKC_PROF_WAIT(1, mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
+          const uint32_t bar = bar_full + 8 * st;
           const uint32_t dst = smem0 + st * stage_bytes;
           mbar_expect_tx(bar, kStageBytes + npad * 512);
           bulk_g2s_hint(dst, src + static_cast<size_t>(s) * kStageBytes, kStageBytes, bar, pol);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
             tma_2d_g2s(dst + kStageBytes + kb * npad * 128, &p.bmap[mi], s * kStageK + kb * 64, wi.y, bar);
+          ++issued;
+          if (++st == NS) { st = 0; ph ^= 1; }
         }
       }
+      OKC_PROF_STORE(0, 0, 1)
       if (!ok) {
         // give copies already issued a bounded chance to land before the CTA retires
-        const int first = it > NS ? it - NS : 0;
-        for (int j = first; j < it; ++j) {
+        const int n = issued < NS ? issued : NS;
+        for (int j = 0; j < n; ++j) {
+          st = (st == 0) ? NS - 1 : st - 1;
+          if (st == NS - 1) ph ^= 1;
           const long long t0 = clock64();
-          while (!mbar_try(smem_u32(&ctrl->full[j % NS]), (j / NS) & 1) && clock64() - t0 < kWaitLimitCycles) {}
+          while (!mbar_try(bar_full + 8 * st, ph) && clock64() - t0 < kWaitLimitCycles) {}
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------ MMA issuers: warp 1 -> first tile
+    // of the pair, warp 2 -> second tile; each owns one accumulator, so the order of additions is fixed
     if (lane == 0) {
-      int it = 0, slot_it = 0, unit_it = 0;
+      const int tile = warp - 1;
+      int st = 0, unit_it = 0;
+      uint32_t ph = 0, sph = 0;     // stage ring phase; A-slot phase (flips once per stage)
       bool ok = true;
+      OKC_PROF_DECL
+      const uint32_t desc_hi = static_cast<uint32_t>(smem_desc_sw128(0) >> 32);
+      const uint32_t desc_lo_const = static_cast<uint32_t>(smem_desc_sw128(0));
       for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x, ++unit_it) {
         const int item = u / p.pairs;
-        const int npad = p.items[item].w;
+        const uint32_t npad = static_cast<uint32_t>(p.items[item].w);
         const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
-        if (!mbar_wait(smem_u32(&ctrl->acc_empty[buf]), ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty)) { ok = false; break; }
+        if (!OKC_PROF_WAIT(2, mbar_wait(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) { ok = false; break; }
         tc_fence_after();
         const uint32_t idesc = idesc_bf16_m128(npad);
-        const uint32_t d0 = tmem + kAccCol0 + buf * 128;
-        const uint32_t d1 = d0 + (nbuf == 2 ? 64 : 128);
+        const uint32_t d = tmem + kAccCol0 + buf * 128 + tile * (nbuf == 2 ? 64 : 128);
+        const uint32_t a_tile = tmem + tile * 32;
+        const uint32_t kb_step = (npad * 128u) >> 4;   // descriptor units between 64-wide K blocks
         uint32_t acc = 0;
-        for (int s = 0; ok && s < p.stages; ++s, ++it) {
-          const int st = it % NS;
-          if (!mbar_wait(smem_u32(&ctrl->full[st]), (it / NS) & 1, abort_flag, kWaitMmaFull)) { ok = false; break; }
-          const uint32_t bsm = smem0 + st * stage_bytes + kStageBytes;
-          for (int kb = 0; kb < 4; ++kb, ++slot_it) {
-            const int sl = slot_it % kASlots;
-            if (!mbar_wait(smem_u32(&ctrl->a_full[sl]), (slot_it / kASlots) & 1, abort_flag, kWaitMmaAFull)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t a0 = tmem + sl * kASlotCols;
-            const uint64_t bd = smem_desc_sw128(bsm + kb * npad * 128);
+        for (int s = 0; ok && s < p.stages; ++s) {
+          if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) { ok = false; break; }
+          uint32_t lo = desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4);
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) {
-              const uint64_t bdk = bd + static_cast<uint64_t>((k4 * 32) >> 4);
-              mma_ts(d0, a0 + k4 * 8, bdk, idesc, acc);
-              mma_ts(d1, a0 + 32 + k4 * 8, bdk, idesc, acc);
-              acc = 1;
+          for (int kb = 0; kb < 4; ++kb) {
+            if (!OKC_PROF_WAIT(4, mbar_wait(bar_afull + 8 * kb, sph, abort_flag, kWaitMmaAFull))) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a0 = a_tile + kb * kASlotCols;
+            if (!OKC_DBG(1)) {
+              mma_ts2(d, a0, lo, desc_hi, idesc, acc);
+              mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
+              mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
+              mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
             }
-            mma_commit(smem_u32(&ctrl->a_empty[sl]));
+            acc = 1;
+            mma_commit(bar_aempty + 8 * kb);
+            lo += kb_step;
           }
-          if (ok) mma_commit(smem_u32(&ctrl->empty[st]));
+          if (ok) mma_commit(bar_empty + 8 * st);
+          sph ^= 1;
+          if (++st == NS) { st = 0; ph ^= 1; }
         }
-        if (ok) mma_commit(smem_u32(&ctrl->acc_full[buf]));
+        if (ok) mma_commit(bar_accfull + 8 * buf);
       }
+      if (warp == 1) { OKC_PROF_STORE(5, 2, 5) }
     }
   } else if (warp >= kDequantWarp0 && warp < kDequantWarp0 + kDequantWarps) {
     // ------------------------------------------------------------ dequantisers
+    // Two groups of 8 warps; group g fills the A slots kb = g and g + 2 of every stage.  Inside a
+    // group a warp is (TMEM lane quarter, tile); a thread dequantises its row's 64 K elements.
     const int dw = warp - kDequantWarp0;
     const int q = warp & 3;               // TMEM lane quarter this warp may touch
     const int tile = (dw >> 2) & 1;       // first or second tile of the pair
-    const int half = dw >> 3;             // which 32-element chunk of a 64-element slot
+    const int grp = dw >> 3;
     const int row = q * 32 + lane;
-    const uint32_t trow = tmem + (static_cast<uint32_t>(q * 32) << 16) + tile * 32 + half * 16;
-    int it = 0, slot_it = 0;
+    const uint32_t trow = tmem + (static_cast<uint32_t>(q * 32) << 16) + tile * 32;
+    const uint32_t code_off = tile * kTileBytes + row * 16;
+    const uint32_t scale_off = tile * kTileBytes + kTileCodeBytes + row * 2;
+    int st = 0;
+    uint32_t ph = 0, sph = 0;
     bool ok = true;
+    OKC_PROF_DECL
     for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
-      for (int s = 0; ok && s < p.stages; ++s, ++it) {
-        const int st = it % NS;
-        if (!mbar_wait(smem_u32(&ctrl->full[st]), (it / NS) & 1, abort_flag, kWaitDqFull)) { ok = false; break; }
-        const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes + tile * kTileBytes;
+      for (int s = 0; ok && s < p.stages; ++s) {
+        if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
         uint4 w[4];
         uint32_t sc[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int chunk = 2 * j + half;
-          w[j] = *reinterpret_cast<const uint4*>(img + chunk * (kTileRows * 16) + row * 16);
-          sc[j] = *reinterpret_cast<const uint16_t*>(img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2);
+          const int chunk = 2 * (grp + 2 * (j >> 1)) + (j & 1);     // kb = grp, grp + 2; both halves
+          w[j] = *reinterpret_cast<const uint4*>(img + code_off + chunk * (kTileRows * 16));
+          sc[j] = *reinterpret_cast<const uint16_t*>(img + scale_off + chunk * (kTileRows * 2));
         }
         // the stage's bytes are in registers: hand the shared-memory slot back
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctrl->empty[st]));
+        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
 #pragma unroll
-        for (int j = 0; j < 4; ++j, ++slot_it) {
-          const int sl = slot_it % kASlots;
-          uint32_t regs[16];
-          dequant_chunk(w[j], sc[j], regs);
-          if (!mbar_wait(smem_u32(&ctrl->a_empty[sl]), ((slot_it / kASlots) & 1) ^ 1, abort_flag, kWaitDqAEmpty)) ok = false;
+        for (int h = 0; h < 2; ++h) {
+          const int kb = grp + 2 * h;
+          uint32_t r0[16], r1[16];
+          if (!OKC_DBG(0)) {
+            dequant_chunk(w[2 * h], sc[2 * h], r0);
+            dequant_chunk(w[2 * h + 1], sc[2 * h + 1], r1);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { r0[i] = w[2 * h].x ^ sc[2 * h]; r1[i] = w[2 * h + 1].y ^ sc[2 * h + 1]; }
+          }
+          if (!OKC_PROF_WAIT(7, mbar_wait(bar_aempty + 8 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) ok = false;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
-          tmem_st16(trow + sl * kASlotCols, regs);
-          tmem_wait_st();
+          if (!OKC_DBG(2)) {
+            tmem_st16(trow + kb * kASlotCols, r0);
+            tmem_st16(trow + kb * kASlotCols + 16, r1);
+            OKC_PROF_VOID(8, tmem_wait_st())
+          } else if (r0[3] == 0x12345678u || r1[5] == 0x12345678u) {
+            p.y[0] = 1.0f;   // keeps the registers alive
+          }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ctrl->a_full[sl]));
+          if (lane == 0) mbar_arrive(bar_afull + 8 * kb);
         }
+        sph ^= 1;
+        if (++st == NS) { st = 0; ph ^= 1; }
       }
     }
+#ifdef OKC_WAIT_PROFILE
+    if (lane == 0 && blockIdx.x < kProfCtas && (warp == kDequantWarp0 || warp == kDequantWarp0 + kDequantWarps - 1)) {
+      const int base = (warp == kDequantWarp0) ? 6 : 10;   // first and last dequantiser warp
+      for (int i = 0; i < 3; ++i) g_wait_prof[MODE][blockIdx.x][base + i] = prof_acc[6 + i];
+      g_wait_prof[MODE][blockIdx.x][base + 3] = clock64() - prof_t0;
+    }
+#endif
   } else if (warp >= kEpilogueWarp0) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
@@ -221,7 +292,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       const int n_rows = wi.z, npad = wi.w;
       const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
       const float sc = p.gs[wi.x] * 256.0f;
-      if (!mbar_wait(smem_u32(&ctrl->acc_full[buf]), (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) ok = false;
+      if (!mbar_wait(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -233,10 +304,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         tmem_ld16(d1 + c0, b);
         tmem_wait_ld();
         if (c0 + 16 >= npad) {
-          // last read of this accumulator: the MMA warp may overwrite it
+          // last read of this accumulator: the MMA warps may overwrite it
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[buf]));
+          if (lane == 0) mbar_arrive(bar_accempty + 8 * buf);
         }
         if (c0 < n_rows) {
 #pragma unroll
@@ -377,6 +448,15 @@ cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t
       reinterpret_cast<const float4*>(in), static_cast<uint2*>(out_bf16), nvec);
   return cudaGetLastError();
 }
+
+#ifdef OKC_WAIT_PROFILE
+// host_out: long long [2][256][16] = per kernel (gate_up, down), per CTA:
+// 0 producer total, 1 producer wait-empty, 2 mma wait acc-empty, 3 mma wait full, 4 mma wait a-full, 5 mma total,
+// 6..9 first dequantiser warp: wait full, wait a-empty, wait tcgen05.st, total; 10..13 the same for the last one.
+extern "C" int okc_moe_debug_wait_profile(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_wait_prof, sizeof(g_wait_prof)) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 size_t gemm_smem_bytes(int n_stages, int ncap) {
   return 1024 + static_cast<size_t>(n_stages) * (kStageBytes + static_cast<size_t>(ncap) * 512) + sizeof(Ctrl);

@@ -55,6 +55,7 @@ struct GemmParams {
   const float* wsorted;
   int H;
   int weighted;
+  int dbg;   // experiment switches, honoured only by the -DOKC_WAIT_PROFILE build (0 otherwise)
 };
 cudaError_t launch_gemm(int mode, const GemmParams& p, int grid, cudaStream_t stream);
 int gemm_stages_for(int ncap);
