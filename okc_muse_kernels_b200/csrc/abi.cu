@@ -233,8 +233,8 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
 
   GemmParams a;
   memset(&a, 0, sizeof(a));
-  const uint32_t boxes[4] = {16, 32, 64, 128};
-  for (int i = 0; i < 4; ++i)
+  const uint32_t boxes[3] = {16, 32, 64};
+  for (int i = 0; i < 3; ++i)
     if (!encode_rows_map(&a.bmap[i], w.xg, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.H), boxes[i])) return OKC_ERR_CUDA;
   a.wpacked = static_cast<const uint8_t*>(packed_w13); a.gs = gs13; a.meta = w.meta; a.items = w.items;
   a.pairs = g.pairs13; a.stages = g.stages13; a.expert_bytes = g.w13_expert_bytes;
@@ -245,7 +245,7 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
 
   GemmParams b;
   memset(&b, 0, sizeof(b));
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 3; ++i)
     if (!encode_rows_map(&b.bmap[i], w.inter, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.I), boxes[i])) return OKC_ERR_CUDA;
   b.wpacked = static_cast<const uint8_t*>(packed_w2); b.gs = gs2; b.meta = w.meta; b.items = w.items;
   b.pairs = g.pairs2; b.stages = g.stages2; b.expert_bytes = g.w2_expert_bytes;

@@ -17,7 +17,7 @@ constexpr int kTileCodeBytes = kChunks * kTileRows * 16;   // 16384
 constexpr int kTileScaleBytes = kChunks * kTileRows * 2;   // 2048
 constexpr int kTileBytes = kTileCodeBytes + kTileScaleBytes;
 constexpr int kStageBytes = 2 * kTileBytes;    // 36864: two tiles (gate+up, or two row tiles of w2)
-constexpr int kChunkRows = 128;                // most rows (tokens) of one work item
+constexpr int kChunkRows = 64;                 // most rows (tokens) of one work item
 constexpr int kMaxSlots = 513;                 // 512 experts + shared
 constexpr int kMaxRoutes = 16384;              // routes (tokens x routes per token) one step may hold
 

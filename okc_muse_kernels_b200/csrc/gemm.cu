@@ -6,16 +6,20 @@
 //   MODE 1  down:    unit = (expert, two adjacent 128-row tiles of w2); epilogue
 //           y[route] = acc * gs * routing weight -> f32, un-permuted to (token, slot) order
 //
-// One persistent CTA per SM, 24 warps:
-//   warp 0        producer: one bulk copy of the 36 KB FP4 stage image + 2-D TMA tiles of the
+// One persistent CTA per SM, 25 warps:
+//   warp 24       producer: one bulk copy of the 36 KB FP4 stage image + 2-D TMA tiles of the
 //                 token operand (128-byte swizzle) per stage, mbarrier ring
-//   warps 1, 2    MMA issuers (one thread each: first / second tile of the pair, so every
-//                 accumulator has one issuer and a fixed order of additions); warp 1 owns the
-//                 TMEM allocation
+//   warps 0..3    MMA issuers, one thread each.  A thread needs ~100 cycles to issue one
+//                 tcgen05.mma whatever its N, and issue from several warps overlaps, so the
+//                 32 MMAs of a stage are spread over four issuers: (tile of the pair) x (parity of
+//                 the 64-wide K block).  Each issuer adds into its own accumulator, which keeps the
+//                 order of additions fixed; the epilogue adds the two parity partials.  Warp 0
+//                 owns the TMEM allocation
 //   warps 4..19   dequantisers in two groups of 8 that take alternate A slots: thread = one weight
 //                 row of one tile; FP4 + E4M3 from shared memory -> bf16x2 registers -> tcgen05.st
 //                 into the 4-slot ring of A operands in TMEM (slot = one 64-wide K block)
-//   warps 20..23  epilogue: tcgen05.ld of the accumulators, scale, activation, store
+//   warps 20..23  epilogue: tcgen05.ld of the accumulators (sum of the partials), scale,
+//                 activation, store
 //
 // The reference computes the same products with mma.sync / wgmma on Hopper
 // (muse_moe_w4a16/submission.py:3828-4014 `tk2f_consume`, :1909-2072 `tw_item`); nothing is shared
@@ -27,11 +31,12 @@
 
 namespace okc {
 
-constexpr int kGemmThreads = 768;
+constexpr int kGemmThreads = 800;      // 25 warps
+constexpr int kIssuers = 4;           // warps 0..3: MMA-issuing threads, (tile of the pair) x (parity of the K block)
 constexpr int kDequantWarp0 = 4;
 constexpr int kDequantWarps = 16;
 constexpr int kEpilogueWarp0 = 20;
-constexpr int kIssuers = 2;           // MMA-issuing threads (one per tile of the pair)
+constexpr int kProducerWarp = 24;
 constexpr int kASlots = 4;            // ring of A operands in TMEM, 64 columns each (K = 64, two tiles)
 constexpr int kASlotCols = 64;
 constexpr int kAccCol0 = 256;         // accumulators live in TMEM columns [256, 512)
@@ -85,7 +90,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int NS = p.n_stages;
-  const int nbuf = (p.ncap <= 64) ? 2 : 1;
+  // accumulators in TMEM columns [256, 512): per buffer four blocks of ncap columns,
+  // (tile 0, even K blocks), (tile 0, odd), (tile 1, even), (tile 1, odd); ncap <= 64
+  const int nbuf = (p.ncap <= 32) ? 2 : 1;            // double-buffered when two sets fit
+  const uint32_t acc_buf_stride = 4u * p.ncap;
   // shared-memory addresses of the barrier arrays (element i is 8 bytes further)
   const uint32_t bar_full = smem_u32(&ctrl->full[0]), bar_empty = smem_u32(&ctrl->empty[0]);
   const uint32_t bar_afull = smem_u32(&ctrl->a_full[0]), bar_aempty = smem_u32(&ctrl->a_empty[0]);
@@ -98,7 +106,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     }
     for (int i = 0; i < kASlots; ++i) {
       mbar_init(bar_afull + 8 * i, kDequantWarps / 2);
-      mbar_init(bar_aempty + 8 * i, kIssuers);
+      mbar_init(bar_aempty + 8 * i, 2);            // the two tiles' issuers of this K block
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_accfull + 8 * i, kIssuers);
@@ -107,7 +115,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     ctrl->abort_code = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == 0) {
     tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
     tmem_relinquish();
   }
@@ -119,10 +127,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   const int n_items = p.meta[kMetaItems];
   const int total_units = n_items * p.pairs;
 
-  if (warp == 0) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      for (int i = 0; i < 4; ++i) tma_prefetch_desc(&p.bmap[i]);
+      for (int i = 0; i < 3; ++i) tma_prefetch_desc(&p.bmap[i]);
       const uint64_t pol = policy_evict_first();
       int st = 0;
       uint32_t ph = 0;
@@ -133,7 +141,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         const int item = u / p.pairs, pair = u - item * p.pairs;
         const int4 wi = p.items[item];
         const int npad = wi.w;
-        const int mi = (npad == 16) ? 0 : (npad == 32) ? 1 : (npad == 64) ? 2 : 3;
+        const int mi = (npad == 16) ? 0 : (npad == 32) ? 1 : 2;
         const uint8_t* src = p.wpacked + static_cast<size_t>(wi.x) * p.expert_bytes +
                              static_cast<size_t>(pair) * p.stages * kStageBytes;
         for (int s = 0; s < p.stages; ++s) {
@@ -161,11 +169,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         }
       }
     }
-  } else if (warp == 1 || warp == 2) {
-    // ------------------------------------------------------------ MMA issuers: warp 1 -> first tile
-    // of the pair, warp 2 -> second tile; each owns one accumulator, so the order of additions is fixed
+  } else if (warp < kIssuers) {
+    // ------------------------------------------------------------ MMA issuers
     if (lane == 0) {
-      const int tile = warp - 1;
+      const int tile = warp & 1, par = warp >> 1;
       int st = 0, unit_it = 0;
       uint32_t ph = 0, sph = 0;     // stage ring phase; A-slot phase (flips once per stage)
       bool ok = true;
@@ -179,27 +186,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         if (!OKC_PROF_WAIT(2, mbar_wait(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) { ok = false; break; }
         tc_fence_after();
         const uint32_t idesc = idesc_bf16_m128(npad);
-        const uint32_t d = tmem + kAccCol0 + buf * 128 + tile * (nbuf == 2 ? 64 : 128);
+        const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + (tile * 2 + par) * p.ncap;
         const uint32_t a_tile = tmem + tile * 32;
         const uint32_t kb_step = (npad * 128u) >> 4;   // descriptor units between 64-wide K blocks
         uint32_t acc = 0;
         for (int s = 0; ok && s < p.stages; ++s) {
           if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) { ok = false; break; }
-          uint32_t lo = desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4);
+          {
+            const uint32_t lo0 = desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4);
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            if (!OKC_PROF_WAIT(4, mbar_wait(bar_afull + 8 * kb, sph, abort_flag, kWaitMmaAFull))) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t a0 = a_tile + kb * kASlotCols;
-            if (!OKC_DBG(1)) {
-              mma_ts2(d, a0, lo, desc_hi, idesc, acc);
-              mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
-              mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
-              mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
+            for (int kb = par; kb < 4; kb += 2) {
+              if (!OKC_PROF_WAIT(4, mbar_wait(bar_afull + 8 * kb, sph, abort_flag, kWaitMmaAFull))) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t a0 = a_tile + kb * kASlotCols;
+              const uint32_t lo = lo0 + kb * kb_step;
+              if (!OKC_DBG(1)) {
+                mma_ts2(d, a0, lo, desc_hi, idesc, acc);
+                mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
+                mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
+                mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
+              }
+              acc = 1;
+              mma_commit(bar_aempty + 8 * kb);
             }
-            acc = 1;
-            mma_commit(bar_aempty + 8 * kb);
-            lo += kb_step;
           }
           if (ok) mma_commit(bar_empty + 8 * st);
           sph ^= 1;
@@ -207,7 +216,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         }
         if (ok) mma_commit(bar_accfull + 8 * buf);
       }
-      if (warp == 1) { OKC_PROF_STORE(5, 2, 5) }
+      if (warp == 0) { OKC_PROF_STORE(5, 2, 5) }
     }
   } else if (warp >= kDequantWarp0 && warp < kDequantWarp0 + kDequantWarps) {
     // ------------------------------------------------------------ dequantisers
@@ -296,13 +305,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * 128;
-      const uint32_t d1 = d0 + (nbuf == 2 ? 64 : 128);
+      const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * acc_buf_stride;     // tile 0, partial 0
+      const uint32_t d1 = d0 + 2 * p.ncap;                                        // tile 1, partial 0
       for (int c0 = 0; c0 < npad; c0 += 16) {
         uint32_t a[16], b[16];
         tmem_ld16(d0 + c0, a);
         tmem_ld16(d1 + c0, b);
-        tmem_wait_ld();
+        {
+          uint32_t a2[16], b2[16];
+          tmem_ld16(d0 + p.ncap + c0, a2);
+          tmem_ld16(d1 + p.ncap + c0, b2);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            a[j] = __float_as_uint(__uint_as_float(a[j]) + __uint_as_float(a2[j]));
+            b[j] = __float_as_uint(__uint_as_float(b[j]) + __uint_as_float(b2[j]));
+          }
+        }
         if (c0 + 16 >= npad) {
           // last read of this accumulator: the MMA warps may overwrite it
           tc_fence_before();
@@ -337,7 +356,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   // ------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }

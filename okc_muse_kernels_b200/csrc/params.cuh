@@ -38,7 +38,7 @@ struct UnpackParams {
 cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t stream);
 
 struct GemmParams {
-  CUtensorMap bmap[4];
+  CUtensorMap bmap[3];      // token operand [rows, K] bf16, box = 64 elements x {16, 32, 64} rows
   const uint8_t* wpacked;
   const float* gs;
   const int32_t* meta;

@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     __syncwarp();
   }
 
-  // ---- 5. work items: experts by load descending (ties by id), cut into runs of <= 128 rows
+  // ---- 5. work items: experts by load descending (ties by id), cut into runs of <= 64 rows
   int active = 0;
   for (int e = tid; e < p.slots; e += kRouteThreads) {
     const int c = cnt[e];

@@ -284,7 +284,7 @@ def test_batch_sweep_rows_match_config2_single_rows(T):
 
 
 def test_zipf_routing_hot_expert_chunks():
-    """Config 5's routing skew at a narrower width: one expert takes > 128 tokens, so its rows are cut
+    """Config 5's routing skew at a narrower width: one expert takes > 64 tokens, twice over, so its rows are cut
     into several work items."""
     dev = _dev()
     wl = synth.Workload("z", 300, 512, 256, 40, 6, zipf_alpha=1.2)
