@@ -78,13 +78,23 @@ inline bool make_geometry(const okc_moe_plan& p, Geometry& g) {
 }
 
 #ifdef __CUDACC__
-// Two E4M3 scale bytes (low byte = block 0) -> bf16x2 {scale0, scale1} * 2^118.
-// byte << 4 is the bf16 whose value is e4m3 * 2^-120 (normal and subnormal codes alike); two
-// exact multiplies bring it to e4m3 * 2^118 (<= 448 * 2^118, finite in bf16).
-__device__ __forceinline__ uint32_t scale_pair_bf16(uint32_t two_bytes) {
-  uint32_t s = ((two_bytes & 0xFFu) | ((two_bytes & 0xFF00u) << 8)) << 4;
-  s = mul_bf16x2(s, 0x7F007F00u);   // * 2^127
+// One E4M3 scale byte -> bf16x2 {scale, scale} * 2^118.
+// byte << 4 is the bf16 whose value is e4m3 * 2^-120 (normal and subnormal codes alike); the
+// multiply by 0x00100010 puts it into both halves (an integer multiply: it runs on the FMA pipe,
+// which has room, rather than on the integer pipe the mask / rotate work saturates).  Two exact
+// bf16 multiplies bring it to e4m3 * 2^118 (<= 448 * 2^118, finite in bf16).
+__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t byte) {
+  uint32_t s = byte * 0x00100010u;
+  s = mul_bf16x2(s, 0x7F007F00u);      // * 2^127
   return mul_bf16x2(s, 0x77007700u);   // * 2^111
+}
+
+// x << k written as a multiply so that it is issued to the FMA pipe.
+template <int K>
+__device__ __forceinline__ uint32_t shl_mul(uint32_t x) {
+  uint32_t d;
+  asm("mul.lo.u32 %0, %1, %2;" : "=r"(d) : "r"(x), "n"(1u << K));
+  return d;
 }
 
 // One 16-code block (w0, w1) and its scale (bf16 broadcast to both halves) -> eight bf16x2
@@ -93,21 +103,18 @@ __device__ __forceinline__ void dequant_block(uint32_t w0, uint32_t w1, uint32_t
   const uint32_t u = (w0 & kLeftMask) | (w1 & ~kLeftMask);
   out[0] = mul_bf16x2(w0 & kOutMask, sc);
   out[1] = mul_bf16x2(rotr32(w0, 4) & kOutMask, sc);
-  out[2] = mul_bf16x2(rotr32(w0, 10) & kOutMask, sc);
+  out[2] = mul_bf16x2(shl_mul<6>(w0) & kOutMask, sc);
   out[3] = mul_bf16x2(rotr32(w1, 2) & kOutMask, sc);
   out[4] = mul_bf16x2(rotr32(w1, 6) & kOutMask, sc);
-  out[5] = mul_bf16x2(rotr32(w1, 12) & kOutMask, sc);
+  out[5] = mul_bf16x2(shl_mul<4>(w1) & kOutMask, sc);
   out[6] = mul_bf16x2(rotr32(u, 8) & kOutMask, sc);
-  out[7] = mul_bf16x2(rotr32(u, 14) & kOutMask, sc);
+  out[7] = mul_bf16x2(shl_mul<2>(u) & kOutMask, sc);
 }
 
-// One 32-code chunk (four words, two scale bytes) -> sixteen bf16x2 registers.
-__device__ __forceinline__ void dequant_chunk(const uint4& w, uint32_t two_scale_bytes, uint32_t (&out)[16]) {
-  const uint32_t s = scale_pair_bf16(two_scale_bytes);
-  const uint32_t s0 = __byte_perm(s, s, 0x1010);
-  const uint32_t s1 = __byte_perm(s, s, 0x3232);
-  dequant_block(w.x, w.y, s0, out);
-  dequant_block(w.z, w.w, s1, out + 8);
+// One 32-code chunk (four words, the two blocks' scale bytes) -> sixteen bf16x2 registers.
+__device__ __forceinline__ void dequant_chunk(const uint4& w, uint32_t scale0, uint32_t scale1, uint32_t (&out)[16]) {
+  dequant_block(w.x, w.y, scale_bf16x2(scale0), out);
+  dequant_block(w.z, w.w, scale_bf16x2(scale1), out + 8);
 }
 #endif
 

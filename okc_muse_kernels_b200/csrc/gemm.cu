@@ -88,7 +88,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_gen + static_cast<size_t>(p.n_stages) * stage_bytes);
   volatile int* abort_flag = &ctrl->abort_code;
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31;
+  // the warp index through a shuffle: the compiler then knows it is the same in every lane and keeps
+  // what is derived from it (roles, barrier addresses, TMEM columns) in uniform registers
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int NS = p.n_stages;
   // accumulators in TMEM columns [256, 512): per buffer four blocks of ncap columns,
   // (tile 0, even K blocks), (tile 0, odd), (tile 1, even), (tile 1, odd); ncap <= 64
@@ -145,7 +148,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         const uint8_t* src = p.wpacked + static_cast<size_t>(wi.x) * p.expert_bytes +
                              static_cast<size_t>(pair) * p.stages * kStageBytes;
         for (int s = 0; s < p.stages; ++s) {
-          if (!OKC_PROF_WAIT(1, mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
+          if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
           const uint32_t bar = bar_full + 8 * st;
           const uint32_t dst = smem0 + st * stage_bytes;
           mbar_expect_tx(bar, kStageBytes + npad * 512);
@@ -183,7 +186,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         const int item = u / p.pairs;
         const uint32_t npad = static_cast<uint32_t>(p.items[item].w);
         const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
-        if (!OKC_PROF_WAIT(2, mbar_wait(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) { ok = false; break; }
+        if (!OKC_PROF_WAIT(2, mbar_wait<500>(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) { ok = false; break; }
         tc_fence_after();
         const uint32_t idesc = idesc_bf16_m128(npad);
         const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + (tile * 2 + par) * p.ncap;
@@ -231,6 +234,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     const uint32_t code_off = tile * kTileBytes + row * 16;
     const uint32_t scale_off = tile * kTileBytes + kTileCodeBytes + row * 2;
     int st = 0;
+    int pending_kb = -1;          // A slot stored to but not yet handed over
     uint32_t ph = 0, sph = 0;
     bool ok = true;
     OKC_PROF_DECL
@@ -241,26 +245,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         if (!ok) break;
         const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
         uint4 w[4];
-        uint32_t sc[4];
+        uint32_t sc[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int chunk = 2 * (grp + 2 * (j >> 1)) + (j & 1);     // kb = grp, grp + 2; both halves
           w[j] = *reinterpret_cast<const uint4*>(img + code_off + chunk * (kTileRows * 16));
-          sc[j] = *reinterpret_cast<const uint16_t*>(img + scale_off + chunk * (kTileRows * 2));
+          sc[2 * j] = img[scale_off + chunk * (kTileRows * 2)];
+          sc[2 * j + 1] = img[scale_off + chunk * (kTileRows * 2) + 1];
         }
         // the stage's bytes are in registers: hand the shared-memory slot back
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+        mbar_arrive_if(bar_empty + 8 * st, lane == 0);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int kb = grp + 2 * h;
           uint32_t r0[16], r1[16];
           if (!OKC_DBG(0)) {
-            dequant_chunk(w[2 * h], sc[2 * h], r0);
-            dequant_chunk(w[2 * h + 1], sc[2 * h + 1], r1);
+            dequant_chunk(w[2 * h], sc[4 * h], sc[4 * h + 1], r0);
+            dequant_chunk(w[2 * h + 1], sc[4 * h + 2], sc[4 * h + 3], r1);
           } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) { r0[i] = w[2 * h].x ^ sc[2 * h]; r1[i] = w[2 * h + 1].y ^ sc[2 * h + 1]; }
+            for (int i = 0; i < 16; ++i) { r0[i] = w[2 * h].x ^ sc[4 * h]; r1[i] = w[2 * h + 1].y ^ sc[4 * h + 2]; }
+          }
+          // the stores of the previous slot completed while this slot was being dequantised:
+          // only now wait for them and hand that slot to the MMA issuers
+          if (pending_kb >= 0) {
+            OKC_PROF_VOID(8, tmem_wait_st())
+            tc_fence_before();
+            __syncwarp();
+            mbar_arrive_if(bar_afull + 8 * pending_kb, lane == 0);
           }
           if (!OKC_PROF_WAIT(7, mbar_wait(bar_aempty + 8 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) ok = false;
           ok = __all_sync(0xffffffffu, ok);
@@ -269,17 +282,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
           if (!OKC_DBG(2)) {
             tmem_st16(trow + kb * kASlotCols, r0);
             tmem_st16(trow + kb * kASlotCols + 16, r1);
-            OKC_PROF_VOID(8, tmem_wait_st())
           } else if (r0[3] == 0x12345678u || r1[5] == 0x12345678u) {
             p.y[0] = 1.0f;   // keeps the registers alive
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_afull + 8 * kb);
+          pending_kb = kb;
         }
         sph ^= 1;
         if (++st == NS) { st = 0; ph ^= 1; }
       }
+    }
+    if (pending_kb >= 0) {
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      mbar_arrive_if(bar_afull + 8 * pending_kb, lane == 0);
     }
 #ifdef OKC_WAIT_PROFILE
     if (lane == 0 && blockIdx.x < kProfCtas && (warp == kDequantWarp0 || warp == kDequantWarp0 + kDequantWarps - 1)) {
@@ -301,7 +317,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       const int n_rows = wi.z, npad = wi.w;
       const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
       const float sc = p.gs[wi.x] * 256.0f;
-      if (!mbar_wait(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) ok = false;
+      if (!mbar_wait<2000>(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -326,7 +342,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
           // last read of this accumulator: the MMA warps may overwrite it
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_accempty + 8 * buf);
+          mbar_arrive_if(bar_accempty + 8 * buf, lane == 0);
         }
         if (c0 < n_rows) {
 #pragma unroll

@@ -7,8 +7,7 @@
 
 namespace okc {
 
-// Cycles a device-side wait may spin before it gives up and reports OKC_ERR_TIMEOUT
-// (about one second at 1.9 GHz).
+// Cycles the producer gives its in-flight copies to land when a CTA gives up (about a second).
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -36,6 +35,15 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive executed under a predicate (no branch around it): `pred` is usually "lane == 0".
+__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, bool pred) {
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "setp.ne.b32 P, %1, 0;\n\t"
+      "@P mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+      ::"r"(bar), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -51,17 +59,23 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the phase did not complete within the cycle limit or when
+// Bounded wait.  Returns false when the phase did not complete within the retry limit or when
 // another role of the CTA already gave up (`*abort_flag` != 0); in the first case it records
-// `code` in `*abort_flag` so that every other role leaves its own waits too.
+// `code` in `*abort_flag` so that every other role leaves its own waits too.  The retry loop is
+// kept to a handful of instructions because retries of waiting warps compete for issue slots with
+// the warps that do the work; roles whose waits are long and not latency-critical (producer,
+// epilogue) pass kSleepNs > 0 and sleep between polls.
+// Limit: a failed try_wait holds the warp for at least tens of cycles, so 2^24 retries are of the
+// order of a second.
+constexpr uint32_t kWaitRetryLimit = 1u << 24;
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  int spins = 0;
+  uint32_t n = 0;
   while (!mbar_try(bar, parity)) {
-    if ((++spins & 63) == 0) {
+    if (kSleepNs > 0) __nanosleep(kSleepNs);
+    if ((++n & 1023u) == 0) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (n >= (kSleepNs > 0 ? (kWaitRetryLimit >> 4) : kWaitRetryLimit)) {
         atomicCAS(const_cast<int*>(abort_flag), 0, code);
         return false;
       }

@@ -6,11 +6,11 @@
 namespace okc {
 
 // Destination bit (word * 32 + bit, inside a two-word block) of bit b of code j: entry j*4 + b.
-// Generated from the rotation plan {w0: 0,4,10; w1: 2,6,12; merged leftovers: 8,14}.
+// Generated from the plan {w0: as is, rotr 4, shl 6; w1: rotr 2, rotr 6, shl 4; merged leftovers: rotr 8, shl 2}.
 __constant__ uint8_t kPairShift[64] = {
-    6,  7,  8,  15, 22, 23, 24, 31, 10, 11, 12, 19, 26, 27, 28, 3,  16, 17, 18, 25, 0,  1,
-    2,  9,  40, 41, 42, 49, 56, 57, 58, 33, 44, 45, 46, 53, 60, 61, 62, 37, 50, 51, 52, 59,
-    34, 35, 36, 43, 14, 47, 48, 55, 30, 63, 32, 39, 20, 21, 54, 29, 4,  5,  38, 13};
+    6, 7, 8, 15, 22, 23, 24, 31, 10, 11, 12, 19, 26, 27, 28, 3, 0, 1, 2, 9, 16, 17, 18, 25, 40, 41,
+    42, 49, 56, 57, 58, 33, 44, 45, 46, 53, 60, 61, 62, 37, 34, 35, 36, 43, 50, 51, 52, 59, 14, 47,
+    48, 55, 30, 63, 32, 39, 4, 5, 38, 13, 20, 21, 54, 29};
 
 
 // One thread per (expert, pair, stage, tile, chunk, row): 16 source bytes + 2 scale bytes.
@@ -64,9 +64,9 @@ __global__ void __launch_bounds__(256) okc_unpack(const UnpackParams p) {
   const uint8_t* img = p.packed + (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes +
                        static_cast<size_t>(tile) * kTileBytes;
   const uint4 w = *reinterpret_cast<const uint4*>(img + chunk * (kTileRows * 16) + row * 16);
-  const uint32_t sc = *reinterpret_cast<const uint16_t*>(img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2);
+  const uint8_t* sc = img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2;
   uint32_t regs[16];
-  dequant_chunk(w, sc, regs);
+  dequant_chunk(w, sc[0], sc[1], regs);
   const int dst_row = p.is_w13 ? (tile * p.inter + pair * kTileRows + row) : (pair * 2 * kTileRows + tile * kTileRows + row);
   uint32_t* dst = reinterpret_cast<uint32_t*>(p.out + static_cast<size_t>(dst_row) * p.K + stage * kStageK + chunk * kChunkK);
 #pragma unroll

@@ -21,12 +21,14 @@ Chunk c of row r holds K elements ``k0 + 32c .. k0 + 32c + 31`` (two 16-element 
 
 Bits inside a word pair
 -----------------------
-The 16 codes of a block are bit-permuted so that eight mask/rotate operations produce eight
+The 16 codes of a block are bit-permuted so that eight shift-and-mask operations produce eight
 bf16x2 registers whose halves are ``code value * 2**-126`` (sign at bit 15, the three magnitude
-bits at bits 8:6 of each half): ``out = rotr(src, s) & 0x81C081C0``.  Six registers come straight
-from ``w0`` (rotations 0, 4, 10) and ``w1`` (rotations 2, 6, 12); the bits those leave over in both
-words are merged with one select, ``u = (w0 & LEFT) | (w1 & ~LEFT)``, and give the last two
-(rotations 8, 14).  ``PAIR_BITS[j][b]`` is the (word, bit) that holds bit ``b`` of code ``j``.
+bits at bits 8:6 of each half): ``out = shift(src) & 0x81C081C0``.  Six registers come straight
+from ``w0`` (as is, rotate right 4, shift left 6) and ``w1`` (rotate right 2 and 6, shift left 4);
+the bits those leave over in both words are merged with one select,
+``u = (w0 & LEFT) | (w1 & ~LEFT)``, and give the last two (rotate right 8, shift left 2).  The left
+shifts are multiplies by a power of two, which run on the FMA pipe instead of the busier integer
+pipe.  ``PAIR_BITS[j][b]`` is the (word, bit) that holds bit ``b`` of code ``j``.
 """
 from __future__ import annotations
 
@@ -42,8 +44,17 @@ TILE_BYTES = TILE_CODE_BYTES + TILE_SCALE_BYTES  # 18432
 STAGE_BYTES = 2 * TILE_BYTES                     # 36864
 
 OUT_MASK = 0x81C081C0
-# (source, rotation) of the eight output registers; source 0 = w0, 1 = w1, 2 = u
-OUT_PLAN = ((0, 0), (0, 4), (0, 10), (1, 2), (1, 6), (1, 12), (2, 8), (2, 14))
+# (source, op, amount) of the eight output registers; source 0 = w0, 1 = w1, 2 = u;
+# op "r" = rotate right, "l" = shift left (bits shifted out are dropped)
+OUT_PLAN = ((0, "r", 0), (0, "r", 4), (0, "l", 6), (1, "r", 2), (1, "r", 6), (1, "l", 4), (2, "r", 8), (2, "l", 2))
+
+
+def _source_bit(op: str, amount: int, target: int) -> int:
+    """Bit of the source word that lands on bit `target` of the shifted word."""
+    if op == "r":
+        return (target + amount) % 32
+    assert target - amount >= 0
+    return target - amount
 # target bit of code bit b (0 = mantissa, 1..2 = exponent, 3 = sign) in the low half of a register
 _HALF_BITS = (6, 7, 8, 15)
 
@@ -51,11 +62,11 @@ _HALF_BITS = (6, 7, 8, 15)
 def _left_mask() -> int:
     """Bits of w0 that its three rotations do not use (the same residues mod 16 in both halves)."""
     used = 0
-    for src, rot in OUT_PLAN:
+    for src, op, amount in OUT_PLAN:
         if src == 0:
             for t in range(32):
                 if (OUT_MASK >> t) & 1:
-                    used |= 1 << ((t + rot) % 32)
+                    used |= 1 << _source_bit(op, amount, t)
     return (~used) & 0xFFFFFFFF
 
 
@@ -65,11 +76,11 @@ LEFT_MASK = _left_mask()
 def _pair_bits():
     table = [[None] * 4 for _ in range(16)]
     seen = set()
-    for i, (src, rot) in enumerate(OUT_PLAN):
+    for i, (src, op, amount) in enumerate(OUT_PLAN):
         for half in range(2):
             j = 2 * i + half
             for b in range(4):
-                p = (_HALF_BITS[b] + 16 * half + rot) % 32
+                p = _source_bit(op, amount, _HALF_BITS[b] + 16 * half)
                 if src == 2:
                     word = 0 if (LEFT_MASK >> p) & 1 else 1
                 else:
@@ -110,7 +121,12 @@ def unpack_block_regs(words: np.ndarray) -> np.ndarray:
     w1 = words[..., 1].astype(np.uint32)
     u = (w0 & np.uint32(LEFT_MASK)) | (w1 & np.uint32(~LEFT_MASK & 0xFFFFFFFF))
     srcs = (w0, w1, u)
-    return np.stack([_rotr(srcs[s], r) & np.uint32(OUT_MASK) for s, r in OUT_PLAN], axis=-1)
+    outs = []
+    for src, op, amount in OUT_PLAN:
+        x = srcs[src]
+        x = _rotr(x, amount) if op == "r" else ((x.astype(np.uint64) << np.uint64(amount)) & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+        outs.append(x & np.uint32(OUT_MASK))
+    return np.stack(outs, axis=-1)
 
 
 def regs_to_values(regs: np.ndarray) -> np.ndarray:
