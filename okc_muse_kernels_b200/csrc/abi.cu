@@ -48,11 +48,7 @@ static std::atomic<int> g_dbg_flags{0};
 #define OKC_DBG_FLAGS 0
 #endif
 
-static int ncap_for(int T) {
-  int n = 16;
-  while (n < T && n < kChunkRows) n <<= 1;
-  return n;
-}
+static int ncap_for(int T) { return chunk_rows_for(T); }
 
 static int sm_count() {
   int dev = 0, n = 0;
@@ -110,7 +106,7 @@ static int route_common(const okc_moe_plan* plan, const float* logits, const int
   p.meta = w.meta; p.counts = w.counts; p.items = w.items; p.sorted = w.sorted; p.pos = w.pos; p.wsorted = w.wsorted;
   p.T = T; p.E = plan->n_experts; p.k = plan->top_k; p.kk = g.kk; p.slots = g.slots;
   p.local_start = plan->local_start; p.local_count = plan->local_count; p.has_shared = plan->shared_inter ? 1 : 0;
-  p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items;
+  p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items; p.chunk_rows = chunk_rows_for(T);
   return launch_route(p, stream) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
 }
 
@@ -233,8 +229,8 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
 
   GemmParams a;
   memset(&a, 0, sizeof(a));
-  const uint32_t boxes[3] = {16, 32, 64};
-  for (int i = 0; i < 3; ++i)
+  const uint32_t boxes[2] = {16, 32};
+  for (int i = 0; i < 2; ++i)
     if (!encode_rows_map(&a.bmap[i], w.xg, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.H), boxes[i])) return OKC_ERR_CUDA;
   a.wpacked = static_cast<const uint8_t*>(packed_w13); a.gs = gs13; a.meta = w.meta; a.items = w.items;
   a.pairs = g.pairs13; a.stages = g.stages13; a.expert_bytes = g.w13_expert_bytes;
@@ -245,7 +241,7 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
 
   GemmParams b;
   memset(&b, 0, sizeof(b));
-  for (int i = 0; i < 3; ++i)
+  for (int i = 0; i < 2; ++i)
     if (!encode_rows_map(&b.bmap[i], w.inter, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.I), boxes[i])) return OKC_ERR_CUDA;
   b.wpacked = static_cast<const uint8_t*>(packed_w2); b.gs = gs2; b.meta = w.meta; b.items = w.items;
   b.pairs = g.pairs2; b.stages = g.stages2; b.expert_bytes = g.w2_expert_bytes;

@@ -17,7 +17,10 @@ constexpr int kTileCodeBytes = kChunks * kTileRows * 16;   // 16384
 constexpr int kTileScaleBytes = kChunks * kTileRows * 2;   // 2048
 constexpr int kTileBytes = kTileCodeBytes + kTileScaleBytes;
 constexpr int kStageBytes = 2 * kTileBytes;    // 36864: two tiles (gate+up, or two row tiles of w2)
-constexpr int kChunkRows = 64;                 // most rows (tokens) of one work item
+constexpr int kChunkRows = 32;                 // most rows (tokens) of one work item
+// Rows per work item for a step of T tokens: 16 for decode-sized steps (the accumulators of eight
+// issuers then fit TMEM twice, so the epilogue overlaps the next unit), 32 beyond.
+__host__ __device__ inline int chunk_rows_for(int T) { return T <= 64 ? 16 : kChunkRows; }
 constexpr int kMaxSlots = 513;                 // 512 experts + shared
 constexpr int kMaxRoutes = 16384;              // routes (tokens x routes per token) one step may hold
 
@@ -62,7 +65,7 @@ inline bool make_geometry(const okc_moe_plan& p, Geometry& g) {
   g.stages2 = g.I / kStageK;
   g.w13_expert_bytes = static_cast<size_t>(g.pairs13) * g.stages13 * kStageBytes;
   g.w2_expert_bytes = static_cast<size_t>(g.pairs2) * g.stages2 * kStageBytes;
-  g.max_items = g.slots + g.R / kChunkRows + 1;
+  g.max_items = g.slots + g.R / 16 + 1;
   size_t o = 0;
   g.off_meta = o;     o = align_up(o + kMetaWords * 4, 256);
   g.off_counts = o;   o = align_up(o + static_cast<size_t>(g.slots + 1) * 4, 256);

@@ -6,19 +6,20 @@
 //   MODE 1  down:    unit = (expert, two adjacent 128-row tiles of w2); epilogue
 //           y[route] = acc * gs * routing weight -> f32, un-permuted to (token, slot) order
 //
-// One persistent CTA per SM, 25 warps:
-//   warp 24       producer: one bulk copy of the 36 KB FP4 stage image + 2-D TMA tiles of the
+// One persistent CTA per SM, 29 warps:
+//   warp 28       producer: one bulk copy of the 36 KB FP4 stage image + 2-D TMA tiles of the
 //                 token operand (128-byte swizzle) per stage, mbarrier ring
-//   warps 0..3    MMA issuers, one thread each.  A thread needs ~100 cycles to issue one
-//                 tcgen05.mma whatever its N, and issue from several warps overlaps, so the
-//                 32 MMAs of a stage are spread over four issuers: (tile of the pair) x (parity of
-//                 the 64-wide K block).  Each issuer adds into its own accumulator, which keeps the
-//                 order of additions fixed; the epilogue adds the two parity partials.  Warp 0
-//                 owns the TMEM allocation
-//   warps 4..19   dequantisers in two groups of 8 that take alternate A slots: thread = one weight
+//   warps 0..7    MMA issuers, one thread each.  A thread needs 100+ cycles to issue one
+//                 tcgen05.mma whatever its N (more when its warp competes for issue slots), and
+//                 issue from several warps overlaps, so the 32 MMAs of a stage are spread over
+//                 eight issuers: (tile of the pair) x (64-wide K block of the stage).  Each issuer
+//                 adds into its own accumulator, which keeps the order of additions fixed; the
+//                 epilogue adds the four K-block partials in a fixed order.  Warp 0 owns the TMEM
+//                 allocation
+//   warps 8..23   dequantisers in two groups of 8 that take alternate A slots: thread = one weight
 //                 row of one tile; FP4 + E4M3 from shared memory -> bf16x2 registers -> tcgen05.st
 //                 into the 4-slot ring of A operands in TMEM (slot = one 64-wide K block)
-//   warps 20..23  epilogue: tcgen05.ld of the accumulators (sum of the partials), scale,
+//   warps 24..27  epilogue: tcgen05.ld of the accumulators (sum of the partials), scale,
 //                 activation, store
 //
 // The reference computes the same products with mma.sync / wgmma on Hopper
@@ -31,12 +32,12 @@
 
 namespace okc {
 
-constexpr int kGemmThreads = 800;      // 25 warps
-constexpr int kIssuers = 4;           // warps 0..3: MMA-issuing threads, (tile of the pair) x (parity of the K block)
-constexpr int kDequantWarp0 = 4;
+constexpr int kGemmThreads = 928;      // 29 warps
+constexpr int kIssuers = 8;           // warps 0..7: MMA-issuing threads, (tile of the pair) x (K block of the stage)
+constexpr int kDequantWarp0 = 8;
 constexpr int kDequantWarps = 16;
-constexpr int kEpilogueWarp0 = 20;
-constexpr int kProducerWarp = 24;
+constexpr int kEpilogueWarp0 = 24;
+constexpr int kProducerWarp = 28;
 constexpr int kASlots = 4;            // ring of A operands in TMEM, 64 columns each (K = 64, two tiles)
 constexpr int kASlotCols = 64;
 constexpr int kAccCol0 = 256;         // accumulators live in TMEM columns [256, 512)
@@ -71,8 +72,8 @@ __device__ long long g_wait_prof[2][kProfCtas][kProfSlots];
 struct Ctrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t a_full[kASlots];
-  uint64_t a_empty[kASlots];
+  uint64_t a_full[2 * kASlots];     // [slot][tile]: the four dequantiser warps of one tile filled the slot
+  uint64_t a_empty[2 * kASlots];    // [slot][tile]: that tile's MMAs on the slot completed
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -93,10 +94,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   // what is derived from it (roles, barrier addresses, TMEM columns) in uniform registers
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int NS = p.n_stages;
-  // accumulators in TMEM columns [256, 512): per buffer four blocks of ncap columns,
-  // (tile 0, even K blocks), (tile 0, odd), (tile 1, even), (tile 1, odd); ncap <= 64
-  const int nbuf = (p.ncap <= 32) ? 2 : 1;            // double-buffered when two sets fit
-  const uint32_t acc_buf_stride = 4u * p.ncap;
+  // accumulators in TMEM columns [256, 512): per buffer eight blocks of ncap columns,
+  // block (tile * 4 + K block of the stage); ncap is 16 (two buffers) or 32 (one)
+  const int nbuf = (p.ncap <= 16) ? 2 : 1;
+  const uint32_t acc_buf_stride = 8u * p.ncap;
   // shared-memory addresses of the barrier arrays (element i is 8 bytes further)
   const uint32_t bar_full = smem_u32(&ctrl->full[0]), bar_empty = smem_u32(&ctrl->empty[0]);
   const uint32_t bar_afull = smem_u32(&ctrl->a_full[0]), bar_aempty = smem_u32(&ctrl->a_empty[0]);
@@ -107,9 +108,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_empty + 8 * i, kDequantWarps + kIssuers);
     }
-    for (int i = 0; i < kASlots; ++i) {
-      mbar_init(bar_afull + 8 * i, kDequantWarps / 2);
-      mbar_init(bar_aempty + 8 * i, 2);            // the two tiles' issuers of this K block
+    for (int i = 0; i < 2 * kASlots; ++i) {
+      mbar_init(bar_afull + 8 * i, 4);             // the four lane quarters of one tile
+      mbar_init(bar_aempty + 8 * i, 1);            // that tile's issuer for this K block
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_accfull + 8 * i, kIssuers);
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      for (int i = 0; i < 3; ++i) tma_prefetch_desc(&p.bmap[i]);
+      for (int i = 0; i < 2; ++i) tma_prefetch_desc(&p.bmap[i]);
       const uint64_t pol = policy_evict_first();
       int st = 0;
       uint32_t ph = 0;
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         const int item = u / p.pairs, pair = u - item * p.pairs;
         const int4 wi = p.items[item];
         const int npad = wi.w;
-        const int mi = (npad == 16) ? 0 : (npad == 32) ? 1 : 2;
+        const int mi = (npad == 16) ? 0 : 1;
         const uint8_t* src = p.wpacked + static_cast<size_t>(wi.x) * p.expert_bytes +
                              static_cast<size_t>(pair) * p.stages * kStageBytes;
         for (int s = 0; s < p.stages; ++s) {
@@ -175,7 +176,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   } else if (warp < kIssuers) {
     // ------------------------------------------------------------ MMA issuers
     if (lane == 0) {
-      const int tile = warp & 1, par = warp >> 1;
+      const int tile = warp & 1, kb = warp >> 1;
+      const uint32_t my_afull = bar_afull + 16 * kb + 8 * tile, my_aempty = bar_aempty + 16 * kb + 8 * tile;
+      const uint32_t a0 = tmem + kb * kASlotCols + tile * 32;
       int st = 0, unit_it = 0;
       uint32_t ph = 0, sph = 0;     // stage ring phase; A-slot phase (flips once per stage)
       bool ok = true;
@@ -189,31 +192,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         if (!OKC_PROF_WAIT(2, mbar_wait<500>(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) { ok = false; break; }
         tc_fence_after();
         const uint32_t idesc = idesc_bf16_m128(npad);
-        const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + (tile * 2 + par) * p.ncap;
-        const uint32_t a_tile = tmem + tile * 32;
-        const uint32_t kb_step = (npad * 128u) >> 4;   // descriptor units between 64-wide K blocks
+        const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + (tile * 4 + kb) * p.ncap;
+        const uint32_t kb_off = kb * ((npad * 128u) >> 4);   // descriptor units to this issuer's K block
         uint32_t acc = 0;
-        for (int s = 0; ok && s < p.stages; ++s) {
+        for (int s = 0; s < p.stages; ++s) {
           if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) { ok = false; break; }
-          {
-            const uint32_t lo0 = desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4);
-#pragma unroll
-            for (int kb = par; kb < 4; kb += 2) {
-              if (!OKC_PROF_WAIT(4, mbar_wait(bar_afull + 8 * kb, sph, abort_flag, kWaitMmaAFull))) { ok = false; break; }
-              tc_fence_after();
-              const uint32_t a0 = a_tile + kb * kASlotCols;
-              const uint32_t lo = lo0 + kb * kb_step;
-              if (!OKC_DBG(1)) {
-                mma_ts2(d, a0, lo, desc_hi, idesc, acc);
-                mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
-                mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
-                mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
-              }
-              acc = 1;
-              mma_commit(bar_aempty + 8 * kb);
-            }
+          const uint32_t lo = (desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4)) + kb_off;
+          if (!OKC_PROF_WAIT(4, mbar_wait(my_afull, sph, abort_flag, kWaitMmaAFull))) { ok = false; break; }
+          tc_fence_after();
+          if (!OKC_DBG(1)) {
+            mma_ts2(d, a0, lo, desc_hi, idesc, acc);
+            mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
+            mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
+            mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
           }
-          if (ok) mma_commit(bar_empty + 8 * st);
+          acc = 1;
+          mma_commit(my_aempty);
+          mma_commit(bar_empty + 8 * st);
           sph ^= 1;
           if (++st == NS) { st = 0; ph ^= 1; }
         }
@@ -244,49 +239,51 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
-        uint4 w[4];
-        uint32_t sc[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int chunk = 2 * (grp + 2 * (j >> 1)) + (j & 1);     // kb = grp, grp + 2; both halves
-          w[j] = *reinterpret_cast<const uint4*>(img + code_off + chunk * (kTileRows * 16));
-          sc[2 * j] = img[scale_off + chunk * (kTileRows * 2)];
-          sc[2 * j + 1] = img[scale_off + chunk * (kTileRows * 2) + 1];
-        }
-        // the stage's bytes are in registers: hand the shared-memory slot back
-        __syncwarp();
-        mbar_arrive_if(bar_empty + 8 * st, lane == 0);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int kb = grp + 2 * h;
-          uint32_t r0[16], r1[16];
+          // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
+          const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb) * (kTileRows * 16));
+          const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb + 1) * (kTileRows * 16));
+          const uint8_t* sp0 = img + scale_off + (2 * kb) * (kTileRows * 2);
+          const uint8_t* sp1 = img + scale_off + (2 * kb + 1) * (kTileRows * 2);
+          const uint32_t s00 = sp0[0], s01 = sp0[1], s10 = sp1[0], s11 = sp1[1];
+          uint32_t r[16];
           if (!OKC_DBG(0)) {
-            dequant_chunk(w[2 * h], sc[4 * h], sc[4 * h + 1], r0);
-            dequant_chunk(w[2 * h + 1], sc[4 * h + 2], sc[4 * h + 3], r1);
+            dequant_chunk(w0, s00, s01, r);
           } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) { r0[i] = w[2 * h].x ^ sc[4 * h]; r1[i] = w[2 * h + 1].y ^ sc[4 * h + 2]; }
+            for (int i = 0; i < 16; ++i) r[i] = w0.x ^ s00;
           }
-          // the stores of the previous slot completed while this slot was being dequantised:
-          // only now wait for them and hand that slot to the MMA issuers
+          // the stores of the previous slot completed while this chunk was being dequantised:
+          // only now wait for them and hand that slot to its MMA issuer
           if (pending_kb >= 0) {
             OKC_PROF_VOID(8, tmem_wait_st())
             tc_fence_before();
             __syncwarp();
-            mbar_arrive_if(bar_afull + 8 * pending_kb, lane == 0);
+            mbar_arrive_if(bar_afull + 16 * pending_kb + 8 * tile, lane == 0);
           }
-          if (!OKC_PROF_WAIT(7, mbar_wait(bar_aempty + 8 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) ok = false;
+          if (!OKC_PROF_WAIT(7, mbar_wait(bar_aempty + 16 * kb + 8 * tile, sph ^ 1, abort_flag, kWaitDqAEmpty))) ok = false;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
+          if (!OKC_DBG(2)) tmem_st16(trow + kb * kASlotCols, r);
+          if (!OKC_DBG(0)) {
+            dequant_chunk(w1, s10, s11, r);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = w1.y ^ s10;
+          }
           if (!OKC_DBG(2)) {
-            tmem_st16(trow + kb * kASlotCols, r0);
-            tmem_st16(trow + kb * kASlotCols + 16, r1);
-          } else if (r0[3] == 0x12345678u || r1[5] == 0x12345678u) {
+            tmem_st16(trow + kb * kASlotCols + 16, r);
+          } else if (r[3] == 0x12345678u) {
             p.y[0] = 1.0f;   // keeps the registers alive
           }
           pending_kb = kb;
         }
+        // the stage's bytes have been consumed: hand the shared-memory slot back
+        __syncwarp();
+        mbar_arrive_if(bar_empty + 8 * st, lane == 0);
         sph ^= 1;
         if (++st == NS) { st = 0; ph ^= 1; }
       }
@@ -295,7 +292,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      mbar_arrive_if(bar_afull + 8 * pending_kb, lane == 0);
+      mbar_arrive_if(bar_afull + 16 * pending_kb + 8 * tile, lane == 0);
     }
 #ifdef OKC_WAIT_PROFILE
     if (lane == 0 && blockIdx.x < kProfCtas && (warp == kDequantWarp0 || warp == kDequantWarp0 + kDequantWarps - 1)) {
@@ -321,21 +318,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * acc_buf_stride;     // tile 0, partial 0
-      const uint32_t d1 = d0 + 2 * p.ncap;                                        // tile 1, partial 0
+      const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * acc_buf_stride;     // tile 0, K block 0
+      const uint32_t d1 = d0 + 4 * p.ncap;                                        // tile 1, K block 0
       for (int c0 = 0; c0 < npad; c0 += 16) {
         uint32_t a[16], b[16];
-        tmem_ld16(d0 + c0, a);
-        tmem_ld16(d1 + c0, b);
         {
-          uint32_t a2[16], b2[16];
-          tmem_ld16(d0 + p.ncap + c0, a2);
-          tmem_ld16(d1 + p.ncap + c0, b2);
-          tmem_wait_ld();
+          // ((K block 0 + 1) + 2) + 3 for each tile: the same order for every shape
+          uint32_t t[16];
+          tmem_ld16(d0 + c0, a);
+          tmem_ld16(d1 + c0, b);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            a[j] = __float_as_uint(__uint_as_float(a[j]) + __uint_as_float(a2[j]));
-            b[j] = __float_as_uint(__uint_as_float(b[j]) + __uint_as_float(b2[j]));
+          for (int part = 1; part < 4; ++part) {
+            tmem_ld16(d0 + part * p.ncap + c0, t);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) a[j] = __float_as_uint(__uint_as_float(a[j]) + __uint_as_float(t[j]));
+            tmem_ld16(d1 + part * p.ncap + c0, t);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) b[j] = __float_as_uint(__uint_as_float(b[j]) + __uint_as_float(t[j]));
           }
         }
         if (c0 + 16 >= npad) {

@@ -16,7 +16,7 @@ struct RouteParams {
   int32_t* sorted;
   int32_t* pos;
   float* wsorted;
-  int T, E, k, kk, slots, local_start, local_count, has_shared, own_t0, own_t1, max_items;
+  int T, E, k, kk, slots, local_start, local_count, has_shared, own_t0, own_t1, max_items, chunk_rows;
 };
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
 cudaError_t launch_gather(const void* hidden, int64_t stride, const int32_t* meta, const int32_t* sorted, int kk,
@@ -38,7 +38,7 @@ struct UnpackParams {
 cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t stream);
 
 struct GemmParams {
-  CUtensorMap bmap[3];      // token operand [rows, K] bf16, box = 64 elements x {16, 32, 64} rows
+  CUtensorMap bmap[2];      // token operand [rows, K] bf16, box = 64 elements x {16, 32} rows
   const uint8_t* wpacked;
   const float* gs;
   const int32_t* meta;

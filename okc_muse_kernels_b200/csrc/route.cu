@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     __syncwarp();
   }
 
-  // ---- 5. work items: experts by load descending (ties by id), cut into runs of <= 64 rows
+  // ---- 5. work items: experts by load descending (ties by id), cut into runs of <= chunk_rows rows
   int active = 0;
   for (int e = tid; e < p.slots; e += kRouteThreads) {
     const int c = cnt[e];
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     int local = 0;
     for (int j = 0; j < per; ++j) {
       const int r = lane * per + j;
-      if (r < n_active) local += (cnt[order[r]] + kChunkRows - 1) / kChunkRows;
+      if (r < n_active) local += (cnt[order[r]] + p.chunk_rows - 1) / p.chunk_rows;
     }
     int incl = local;
 #pragma unroll
@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     int run = incl - local;
     for (int j = 0; j < per; ++j) {
       const int r = lane * per + j;
-      if (r < n_active) { ibase[r] = run; run += (cnt[order[r]] + kChunkRows - 1) / kChunkRows; }
+      if (r < n_active) { ibase[r] = run; run += (cnt[order[r]] + p.chunk_rows - 1) / p.chunk_rows; }
     }
     if (lane == 31) {
       p.meta[kMetaItems] = incl < p.max_items ? incl : p.max_items;
@@ -208,8 +208,8 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     const int e = order[r];
     const int c = cnt[e];
     int it = ibase[r];
-    for (int c0 = 0; c0 < c && it < p.max_items; c0 += kChunkRows, ++it) {
-      const int n = min(kChunkRows, c - c0);
+    for (int c0 = 0; c0 < c && it < p.max_items; c0 += p.chunk_rows, ++it) {
+      const int n = min(p.chunk_rows, c - c0);
       int npad = 16;
       while (npad < n) npad <<= 1;
       p.items[it] = make_int4(e, offs[e] + c0, n, npad);

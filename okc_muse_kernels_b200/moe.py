@@ -266,7 +266,7 @@ def sorted_routes(state: dict, T: int, max_items: int | None = None) -> dict:
     sz = plan.sizes()
     dev = state["workspace"].device
     R = T * sz.routes_per_token
-    max_items = max_items or (sz.expert_slots + R // 64 + 1)
+    max_items = max_items or (sz.expert_slots + R // 16 + 1)
     counts = torch.empty(sz.expert_slots, dtype=torch.int32, device=dev)
     srt = torch.empty(R, dtype=torch.int32, device=dev)
     pos = torch.empty(R, dtype=torch.int32, device=dev)

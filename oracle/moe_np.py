@@ -75,7 +75,7 @@ def route_sigmoid_topk(logits: np.ndarray, bias: np.ndarray, k: int, multiplier:
     return ids, w
 
 
-def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int = 64):
+def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int = 16):
     """Token -> expert sort of the local routes.
 
     Route index i = t*k + slot.  Returns a dict with
