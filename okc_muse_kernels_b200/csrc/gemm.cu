@@ -235,9 +235,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     OKC_PROF_DECL
     for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
       for (int s = 0; ok && s < p.stages; ++s) {
+        // a lane whose wait ran out is caught by the vote before the first tensor-memory store below
         if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) ok = false;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
         const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -520,7 +519,37 @@ cudaError_t launch_gemm(int mode, const GemmParams& p, int grid, cudaStream_t st
   return cudaGetLastError();
 }
 
+// The combine without the post-expert norm needs no row-wide reduction, so a token's row is cut
+// into 1024-column slices over blockIdx.y: four times as many CTAs as tokens keep the small launch
+// from being latency-bound.  Same sums in the same (slot) order as okc_combine.
+__global__ void __launch_bounds__(kCombineThreads) okc_combine_sliced(const CombineParams p) {
+  const int t = blockIdx.x;
+  const int v = blockIdx.y * kCombineThreads + threadIdx.x;   // float4 index within the row
+  if (v >= p.H / 4) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < p.kk; ++s) {
+    if (p.pos[t * p.kk + s] < 0) continue;
+    const float4 a = reinterpret_cast<const float4*>(p.y + static_cast<size_t>(t * p.kk + s) * p.H)[v];
+    acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+  }
+  if (p.out_f32) {
+    reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(t) * p.H)[v] = acc;
+  } else {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(t) * p.H)[v] = o;
+  }
+}
+
 cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream) {
+  if (p.post_w == nullptr) {
+    const dim3 grid(T, (p.H / 4 + kCombineThreads - 1) / kCombineThreads);
+    okc_combine_sliced<<<grid, kCombineThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+  }
   okc_combine<<<T, kCombineThreads, 0, stream>>>(p);
   return cudaGetLastError();
 }
