@@ -128,6 +128,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   tc_fence_after();
   const uint32_t tmem = ctrl->tmem_base;
 
+  // everything above overlapped the tail of the kernel before; its outputs are read from here on
+  griddep_wait();
+  griddep_launch_dependents();
   const int n_items = p.meta[kMetaItems];
   const int total_units = n_items * p.pairs;
 
@@ -390,6 +393,7 @@ constexpr int kCombineThreads = 256;
 constexpr int kCombineMaxPer = 8;   // float4 per thread: H <= 256 * 4 * 8 = 8192
 
 __global__ void __launch_bounds__(kCombineThreads) okc_combine(const CombineParams p) {
+  griddep_wait();
   const int t = blockIdx.x, tid = threadIdx.x;
   const int nvec = p.H / 4;
   float4 acc[kCombineMaxPer];
@@ -510,11 +514,13 @@ cudaError_t launch_gemm(int mode, const GemmParams& p, int grid, cudaStream_t st
   if (mode == 0) {
     e = cudaFuncSetAttribute(okc_grouped_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    okc_grouped_gemm<0><<<grid, kGemmThreads, smem, stream>>>(p);
+    e = launch_kernel(okc_grouped_gemm<0>, dim3(grid), dim3(kGemmThreads), smem, stream, true, p);
+    if (e != cudaSuccess) return e;
   } else {
     e = cudaFuncSetAttribute(okc_grouped_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    okc_grouped_gemm<1><<<grid, kGemmThreads, smem, stream>>>(p);
+    e = launch_kernel(okc_grouped_gemm<1>, dim3(grid), dim3(kGemmThreads), smem, stream, true, p);
+    if (e != cudaSuccess) return e;
   }
   return cudaGetLastError();
 }
@@ -523,6 +529,7 @@ cudaError_t launch_gemm(int mode, const GemmParams& p, int grid, cudaStream_t st
 // into 1024-column slices over blockIdx.y: four times as many CTAs as tokens keep the small launch
 // from being latency-bound.  Same sums in the same (slot) order as okc_combine.
 __global__ void __launch_bounds__(kCombineThreads) okc_combine_sliced(const CombineParams p) {
+  griddep_wait();
   const int t = blockIdx.x;
   const int v = blockIdx.y * kCombineThreads + threadIdx.x;   // float4 index within the row
   if (v >= p.H / 4) return;
@@ -547,10 +554,9 @@ __global__ void __launch_bounds__(kCombineThreads) okc_combine_sliced(const Comb
 cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream) {
   if (p.post_w == nullptr) {
     const dim3 grid(T, (p.H / 4 + kCombineThreads - 1) / kCombineThreads);
-    okc_combine_sliced<<<grid, kCombineThreads, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_kernel(okc_combine_sliced, grid, dim3(kCombineThreads), 0, stream, true, p);
   }
-  okc_combine<<<T, kCombineThreads, 0, stream>>>(p);
+  return launch_kernel(okc_combine, dim3(T), dim3(kCombineThreads), 0, stream, true, p);
   return cudaGetLastError();
 }
 

@@ -1,5 +1,7 @@
 // Kernel parameter blocks and host launchers shared by the translation units of the library.
 #pragma once
+#include <utility>
+
 #include "format.cuh"
 
 namespace okc {
@@ -72,6 +74,23 @@ cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream);
 
 cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t stream);
 size_t route_smem_bytes(int R, int slots);
+
+// Launch with (pdl = true) or without the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 size_t gemm_smem_bytes(int n_stages, int ncap);
 
 }  // namespace okc

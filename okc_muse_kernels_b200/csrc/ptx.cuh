@@ -194,6 +194,14 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while the kernel
+// before it in the stream is still running; griddep_wait() blocks until that kernel has completed
+// and its writes are visible (it returns at once for a normally launched kernel).  Everything a
+// kernel does before the wait (barrier set-up, TMEM allocation) overlaps the predecessor's tail.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- small math
 __device__ __forceinline__ uint32_t rotr32(uint32_t x, int s) { return __funnelshift_r(x, x, s); }
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {

@@ -222,6 +222,8 @@ __global__ void __launch_bounds__(128) okc_gather_rows(const uint16_t* __restric
                                                        const int32_t* __restrict__ meta,
                                                        const int32_t* __restrict__ sorted, int kk, int H,
                                                        uint16_t* __restrict__ xg) {
+  griddep_wait();   // the sort tables come from the kernel before
+  griddep_launch_dependents();
   const int q = blockIdx.x;
   if (q >= meta[kMetaLocalRoutes]) return;
   const int t = sorted[q] / kk;
@@ -244,9 +246,8 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
 
 cudaError_t launch_gather(const void* hidden, int64_t stride, const int32_t* meta, const int32_t* sorted, int kk,
                           int H, int R, void* xg, cudaStream_t stream) {
-  okc_gather_rows<<<R, 128, 0, stream>>>(static_cast<const uint16_t*>(hidden), stride, meta, sorted, kk, H,
-                                         static_cast<uint16_t*>(xg));
-  return cudaGetLastError();
+  return launch_kernel(okc_gather_rows, dim3(R), dim3(128), 0, stream, true, static_cast<const uint16_t*>(hidden),
+                       stride, meta, sorted, kk, H, static_cast<uint16_t*>(xg));
 }
 
 }  // namespace okc
