@@ -179,6 +179,13 @@ int okc_moe_unpack_bf16(const okc_moe_plan* plan, const void* packed, int which,
  * OKC_ERR_TIMEOUT with *detail = a code naming the wait that ran out. */
 int okc_moe_read_status(const void* workspace, okc_stream_t stream, int32_t* detail);
 
+/* Failure-detection self test: launches one warp that waits, with a short limit, on a barrier
+ * nothing will ever complete.  The wait runs out, the kernel returns normally and sets the status
+ * words of `workspace` the way a GEMM kernel whose wait ran out does: okc_moe_read_status then
+ * returns OKC_ERR_TIMEOUT with detail 0x7e.  The next okc_moe_route / okc_moe_sort call clears
+ * the status.  The reference's waits are unbounded spins (submission.py:3862-3869, 394-398). */
+int okc_moe_probe_wait_timeout(void* workspace, okc_stream_t stream);
+
 /* Kernels launched by the last okc_moe_experts / okc_moe_step shape: a constant of the build. */
 int okc_moe_launches_per_step(void);
 

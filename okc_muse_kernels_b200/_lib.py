@@ -55,6 +55,7 @@ SIGNATURES = {
                                               _P, _P, C.c_int, _P]),
     "okc_moe_export_sort": (C.c_int, [_PLAN, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P]),
     "okc_moe_unpack_bf16": (C.c_int, [_PLAN, _P, C.c_int, C.c_int, _P, _P]),
+    "okc_moe_probe_wait_timeout": (C.c_int, [_P, _P]),
     "okc_moe_read_status": (C.c_int, [_P, _P, C.POINTER(C.c_int32)]),
 }
 

@@ -325,6 +325,13 @@ int okc_moe_export_sort(const okc_moe_plan* plan, const void* workspace, int T, 
   return e == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
 }
 
+int okc_moe_probe_wait_timeout(void* workspace, okc_stream_t stream) {
+  if (!workspace) return OKC_ERR_BAD_ARG;
+  int32_t* meta = static_cast<int32_t*>(workspace);
+  return launch_wait_timeout_probe(meta + kMetaStatus, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK
+                                                                                                             : OKC_ERR_CUDA;
+}
+
 int okc_moe_read_status(const void* workspace, okc_stream_t stream_, int32_t* detail) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!workspace) return OKC_ERR_BAD_ARG;

@@ -73,6 +73,7 @@ struct CombineParams {
 cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream);
 
 cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t stream);
+cudaError_t launch_wait_timeout_probe(int32_t* status, cudaStream_t stream);
 size_t route_smem_bytes(int R, int slots);
 
 // Launch with (pdl = true) or without the programmatic-serialization attribute.

@@ -69,13 +69,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // order of a second.
 constexpr uint32_t kWaitRetryLimit = 1u << 24;
 template <int kSleepNs = 0>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          uint32_t retry_limit = kWaitRetryLimit) {
   uint32_t n = 0;
   while (!mbar_try(bar, parity)) {
     if (kSleepNs > 0) __nanosleep(kSleepNs);
     if ((++n & 1023u) == 0) {
       if (*abort_flag != 0) return false;
-      if (n >= (kSleepNs > 0 ? (kWaitRetryLimit >> 4) : kWaitRetryLimit)) {
+      if (n >= (kSleepNs > 0 ? (retry_limit >> 4) : retry_limit)) {
         atomicCAS(const_cast<int*>(abort_flag), 0, code);
         return false;
       }

@@ -232,6 +232,31 @@ __global__ void __launch_bounds__(128) okc_gather_rows(const uint16_t* __restric
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+// Exercises the bounded wait on purpose: one warp waits on an mbarrier that nothing ever arrives
+// on, with a short retry limit; the wait gives up and the kernel reports it through the status
+// words exactly as the GEMM kernels do (no trap, the context stays usable).
+__global__ void okc_wait_timeout_probe(int32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_code;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_code = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_code, 0x7e, 1u << 14);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    status[0] = ok ? OKC_OK : OKC_ERR_TIMEOUT;
+    status[1] = abort_code;
+  }
+}
+
+cudaError_t launch_wait_timeout_probe(int32_t* status, cudaStream_t stream) {
+  okc_wait_timeout_probe<<<1, 32, 0, stream>>>(status);
+  return cudaGetLastError();
+}
+
 size_t route_smem_bytes(int R, int slots) {
   return sizeof(int32_t) * (static_cast<size_t>(R) + kRouteWarps * slots + slots + 3 * (slots + 1));
 }

@@ -85,6 +85,35 @@ def make_weights(w: Workload, seed: int = 5252, device: str | torch.device = "cu
     return out
 
 
+def make_reference_style_weights(n_experts: int, hidden: int, inter: int, seed: int,
+                                 device: str | torch.device = "cuda", wide_scales: bool = False) -> dict:
+    """NVFP4 weights with the distribution of the reference's own generator
+    (muse_moe_w4a16/nvfp4.py:105-128, reference.py:33-50): codes uniform over all 16 patterns,
+    block scales log-normal (log2 ~ N(7, 0.4), clamped to [8, 448]) or, with wide_scales,
+    log-uniform over 2^-6 .. 448; one global scale per tensor that normalises dot products to about
+    unit variance; a post-expert norm weight 0.1 * N(0, 1)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def tensor(rows: int, k: int):
+        codes = torch.randint(0, 256, (n_experts, rows, k // 2), dtype=torch.uint8, generator=g, device=device)
+        if wide_scales:
+            u = torch.rand((n_experts, rows, k // 16), generator=g, device=device)
+            sf = torch.exp2(-6 + u * (8.807354922057604 + 6)).to(torch.float8_e4m3fn)      # log2(448) = 8.807...
+            mean_sq = float(sf.float().pow(2).mean())
+        else:
+            z = torch.randn((n_experts, rows, k // 16), generator=g, device=device)
+            sf = torch.exp2(7.0 + 0.4 * z).clamp(8.0, 448.0).to(torch.float8_e4m3fn)
+            mean_sq = 4.0 ** 7.0 * 2.718281828459045 ** (2 * (0.6931471805599453 * 0.4) ** 2)
+        gs = torch.full((n_experts,), 1.0 / (8.6 * mean_sq * k) ** 0.5, dtype=torch.float32, device=device)
+        return codes, sf, gs
+
+    w13, w13_sf, w13_gs = tensor(2 * inter, hidden)
+    w2, w2_sf, w2_gs = tensor(hidden, inter)
+    post = (0.1 * torch.randn((hidden,), generator=g, device=device)).to(torch.bfloat16)
+    return {"w13": w13, "w13_sf": w13_sf, "w13_gs": w13_gs, "w2": w2, "w2_sf": w2_sf, "w2_gs": w2_gs,
+            "post_norm_w": post}
+
+
 def make_inputs(w: Workload, seed: int, device: str | torch.device = "cuda", tokens: int | None = None):
     """hidden ~ N(0,1) bf16 [T, H]; router logits ~ N(0,1) f32 [T, E] (+ log-popularity bias with
     popularity ~ rank^-alpha over a seeded expert permutation when the workload is Zipf)."""
