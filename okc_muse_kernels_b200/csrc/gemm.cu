@@ -238,8 +238,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     OKC_PROF_DECL
     for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
       for (int s = 0; ok && s < p.stages; ++s) {
-        // a lane whose wait ran out is caught by the vote before the first tensor-memory store below
-        if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) ok = false;
+        if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) { ok = false; break; }
         const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -247,9 +246,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
           // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
           const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb) * (kTileRows * 16));
           const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb + 1) * (kTileRows * 16));
-          const uint8_t* sp0 = img + scale_off + (2 * kb) * (kTileRows * 2);
-          const uint8_t* sp1 = img + scale_off + (2 * kb + 1) * (kTileRows * 2);
-          const uint32_t s00 = sp0[0], s01 = sp0[1], s10 = sp1[0], s11 = sp1[1];
+          const uint32_t sp0 = smem0 + st * stage_bytes + scale_off + (2 * kb) * (kTileRows * 2);
+          const uint32_t sp1 = sp0 + kTileRows * 2;
+          const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
           uint32_t r[16];
           if (!OKC_DBG(0)) {
             dequant_chunk(w0, s00, s01, r);
@@ -265,8 +264,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
             __syncwarp();
             mbar_arrive_if(bar_afull + 16 * pending_kb + 8 * tile, lane == 0);
           }
+          // every lane polls the same barrier in the same instruction, so the outcome is the same
+          // in all of them and the warp stays converged for the tensor-memory stores below
           if (!OKC_PROF_WAIT(7, mbar_wait(bar_aempty + 16 * kb + 8 * tile, sph ^ 1, abort_flag, kWaitDqAEmpty))) ok = false;
-          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
           if (!OKC_DBG(2)) tmem_st16(trow + kb * kASlotCols, r);
@@ -316,9 +316,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       const int n_rows = wi.z, npad = wi.w;
       const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
       const float sc = p.gs[wi.x] * 256.0f;
-      if (!mbar_wait<2000>(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) ok = false;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!mbar_wait<2000>(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * acc_buf_stride;     // tile 0, K block 0
       const uint32_t d1 = d0 + 4 * p.ncap;                                        // tile 1, K block 0

@@ -71,18 +71,29 @@ constexpr uint32_t kWaitRetryLimit = 1u << 24;
 template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
                                           uint32_t retry_limit = kWaitRetryLimit) {
-  uint32_t n = 0;
-  while (!mbar_try(bar, parity)) {
-    if (kSleepNs > 0) __nanosleep(kSleepNs);
-    if ((++n & 1023u) == 0) {
-      if (*abort_flag != 0) return false;
-      if (n >= (kSleepNs > 0 ? (retry_limit >> 4) : retry_limit)) {
-        atomicCAS(const_cast<int*>(abort_flag), 0, code);
-        return false;
-      }
+  if (mbar_try(bar, parity)) return true;
+  const uint32_t limit = kSleepNs > 0 ? (retry_limit >> 4) : retry_limit;
+  // eight polls per pass of the loop: the retry counter and the abort check cost integer-pipe
+  // instructions, which is what the dequantising warps next to a waiting warp are short of
+#pragma unroll 1
+  for (uint32_t n = 0; n < limit; n += 8) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (kSleepNs > 0) __nanosleep(kSleepNs);
+      if (mbar_try(bar, parity)) return true;
     }
+    if (*abort_flag != 0) return false;
   }
-  return true;
+  atomicCAS(const_cast<int*>(abort_flag), 0, code);
+  return false;
+}
+
+// One byte from shared memory, as its own load: two adjacent byte loads are otherwise merged into a
+// wider load plus byte extractions on the integer pipe, which is busier than the load pipe here.
+__device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
+  return v;
 }
 
 // ---------------------------------------------------------------- TMA
