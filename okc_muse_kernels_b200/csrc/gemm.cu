@@ -76,6 +76,7 @@ struct Ctrl {
   uint64_t a_empty[2 * kASlots];    // [slot][tile]: that tile's MMAs on the slot completed
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t dummy;                   // arrived on, never waited on
   uint32_t tmem_base;
   int abort_code;
 };
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       mbar_init(bar_accfull + 8 * i, kIssuers);
       mbar_init(bar_accempty + 8 * i, 4);
     }
+    mbar_init(smem_u32(&ctrl->dummy), 1);
     ctrl->abort_code = 0;
     mbar_fence_init();
   }
@@ -231,22 +233,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     const uint32_t trow = tmem + (static_cast<uint32_t>(q * 32) << 16) + tile * 32;
     const uint32_t code_off = tile * kTileBytes + row * 16;
     const uint32_t scale_off = tile * kTileBytes + kTileCodeBytes + row * 2;
+    const uint32_t my_afull = bar_afull + 8 * tile, my_aempty = bar_aempty + 8 * tile;
+    const bool lane0 = lane == 0;
+    // this role only counts stages: units handled by this CTA x stages per unit
+    const int my_units = (static_cast<int>(blockIdx.x) < total_units)
+                             ? (total_units - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                             : 0;
+    const int total_stages = my_units * p.stages;
     int st = 0;
-    int pending_kb = -1;          // A slot stored to but not yet handed over
+    // barrier of the A slot stored to but not yet handed over; a barrier nobody waits on stands in
+    // before the first slot, so the hand-over below needs no "is anything pending" test
+    uint32_t pend_bar = smem_u32(&ctrl->dummy);
     uint32_t ph = 0, sph = 0;
-    bool ok = true;
     OKC_PROF_DECL
-    for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
-      for (int s = 0; ok && s < p.stages; ++s) {
-        if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) { ok = false; break; }
+    for (int it = 0; it < total_stages; ++it) {
+      if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) goto dq_done;
+      {
         const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
+        const uint32_t simg = smem0 + st * stage_bytes + scale_off;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int kb = grp + 2 * h;
           // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
           const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb) * (kTileRows * 16));
           const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb + 1) * (kTileRows * 16));
-          const uint32_t sp0 = smem0 + st * stage_bytes + scale_off + (2 * kb) * (kTileRows * 2);
+          const uint32_t sp0 = simg + (2 * kb) * (kTileRows * 2);
           const uint32_t sp1 = sp0 + kTileRows * 2;
           const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
           uint32_t r[16];
@@ -258,16 +269,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
           }
           // the stores of the previous slot completed while this chunk was being dequantised:
           // only now wait for them and hand that slot to its MMA issuer
-          if (pending_kb >= 0) {
-            OKC_PROF_VOID(8, tmem_wait_st())
-            tc_fence_before();
-            __syncwarp();
-            mbar_arrive_if(bar_afull + 16 * pending_kb + 8 * tile, lane == 0);
-          }
+          OKC_PROF_VOID(8, tmem_wait_st())
+          tc_fence_before();
+          mbar_arrive_if(pend_bar, lane0);
           // every lane polls the same barrier in the same instruction, so the outcome is the same
           // in all of them and the warp stays converged for the tensor-memory stores below
-          if (!OKC_PROF_WAIT(7, mbar_wait(bar_aempty + 16 * kb + 8 * tile, sph ^ 1, abort_flag, kWaitDqAEmpty))) ok = false;
-          if (!ok) break;
+          if (!OKC_PROF_WAIT(7, mbar_wait(my_aempty + 16 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) goto dq_done;
           tc_fence_after();
           if (!OKC_DBG(2)) tmem_st16(trow + kb * kASlotCols, r);
           if (!OKC_DBG(0)) {
@@ -281,21 +288,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
           } else if (r[3] == 0x12345678u) {
             p.y[0] = 1.0f;   // keeps the registers alive
           }
-          pending_kb = kb;
+          pend_bar = my_afull + 16 * kb;
         }
-        // the stage's bytes have been consumed: hand the shared-memory slot back
-        __syncwarp();
-        mbar_arrive_if(bar_empty + 8 * st, lane == 0);
-        sph ^= 1;
-        if (++st == NS) { st = 0; ph ^= 1; }
       }
+      // the stage's bytes have been consumed (the loads fed the arithmetic above): hand the
+      // shared-memory slot back
+      mbar_arrive_if(bar_empty + 8 * st, lane0);
+      sph ^= 1;
+      if (++st == NS) { st = 0; ph ^= 1; }
     }
-    if (pending_kb >= 0) {
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      mbar_arrive_if(bar_afull + 16 * pending_kb + 8 * tile, lane == 0);
-    }
+  dq_done:
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive_if(pend_bar, lane0);
 #ifdef OKC_WAIT_PROFILE
     if (lane == 0 && blockIdx.x < kProfCtas && (warp == kDequantWarp0 || warp == kDequantWarp0 + kDequantWarps - 1)) {
       const int base = (warp == kDequantWarp0) ? 6 : 10;   // first and last dequantiser warp
