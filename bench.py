@@ -229,9 +229,35 @@ def run_gpu(args):
                 okc.moe_step(h, lg, state, out=o)
             graphs.append(g)
 
+    ep_timing = "eager launches + NCCL collectives per step"
+    if world > 1:
+        # the expert-parallel step (two all-gathers, five kernels, a reduce-scatter, a cast) as one CUDA
+        # graph per routing seed: at 8 ranks a rank's kernels take about as long as the host needs to
+        # launch them one by one.  Every rank captures; if capture is refused the step stays eager.
+        own = [(h[t0:t1].contiguous(), lg[t0:t1].contiguous()) for h, lg in inputs]
+        for ho, lo in own:
+            layer.step(ho, lo)
+        torch.cuda.synchronize()
+        dist.barrier()
+        try:
+            for ho, lo in own:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    layer.step(ho, lo)
+                graphs.append(g)
+            ep_timing = "CUDA-graph replay per step (kernels + NCCL collectives captured)"
+        except Exception as exc:      # noqa: BLE001 - any capture failure means: run eagerly
+            graphs = []
+            print(f"rank {rank}: graph capture of the expert-parallel step failed ({exc}); running eagerly", file=sys.stderr)
+        ok_flag = torch.tensor([1 if graphs else 0], device=dev)
+        dist.all_reduce(ok_flag, op=dist.ReduceOp.MIN)
+        if int(ok_flag.item()) == 0:
+            graphs = []
+            ep_timing = "eager launches + NCCL collectives per step"
+
     def step(i):
         j = i % len(SEEDS)
-        if world == 1:
+        if graphs:
             graphs[j].replay()
         else:
             h, lg = inputs[j]
@@ -382,7 +408,7 @@ def run_gpu(args):
                 "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": _workload_name(wl, tokens, world),
                            "l2": "touched weights per step exceed L2 (126 MB) and a 256 MB buffer is read between timed steps",
-                           "timing": "CUDA-graph replay per step" if world == 1 else "eager launches + NCCL collectives per step",
+                           "timing": "CUDA-graph replay per step" if world == 1 else ep_timing,
                            "touched_experts_per_seed": touched, "routing_seeds": list(SEEDS)},
                 "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
                 "gpu_launches": _lib.lib().okc_moe_launches_per_step() * args.steps + (args.steps if world > 1 else 0),
