@@ -30,6 +30,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# dram bytes of one okc_moe_gemm launch under ncu, configuration 2 with 115 touched experts
+NCU_TRAFFIC_C2_115 = 820.4e6 + 413.3e6
 SEEDS = (7, 8, 9)
 METRIC = "moe_step_weight_stream_bandwidth"
 UNIT = "GB/s"
@@ -308,9 +310,9 @@ def run_gpu(args):
     ms_per_step = total_ms / args.steps
     value = step_bytes / (total_ms * 1e-3) / 1e9
 
-    # ---- roofline of the dominant kernel (gate_up GEMM), CUDA events around each kernel
+    # ---- roofline of the dominant kernel (the grouped-GEMM launch), CUDA events around each kernel
     roof = None
-    phases = {"gather": [], "gate_up": [], "down": [], "combine": []}
+    phases = {"gather": [], "gemm": [], "combine": [], "total": []}
     prof_out = torch.empty((tokens, wl.hidden), dtype=torch.float32 if world > 1 else torch.bfloat16, device=dev)
     n_prof = max(3, min(args.steps, 12))
     gate_up_bytes = []
@@ -325,16 +327,17 @@ def run_gpu(args):
             for k in phases:
                 phases[k].append(ms[k])
             n_exp = touched[j] + (1 if wl.shared_inter else 0)
-            gate_up_bytes.append(n_exp * 2 * wl.inter * wl.hidden * 9 // 16 + touched[j] * 0 + tokens * wl.top_k * wl.hidden * 2)
-    gu_ms = statistics.mean(phases["gate_up"])
+            # weight stream of both GEMMs (4 bits + 1/16 scale byte per element) + the gathered token rows
+            gate_up_bytes.append(n_exp * 3 * wl.inter * wl.hidden * 9 // 16 + tokens * wl.top_k * wl.hidden * 2)
+    gu_ms = statistics.mean(phases["gemm"])
     achieved = statistics.mean(gate_up_bytes) / (gu_ms * 1e-3) / 1e9
-    # DRAM traffic of one gate_up launch from the ncu capture summarised under profiles/
-    # (dram__bytes_read.sum + dram__bytes_write.sum = 820.4 MB at 115 touched experts of configuration 2),
+    # DRAM traffic of one launch from the ncu capture summarised under profiles/
+    # (dram__bytes_read.sum + dram__bytes_write.sum at 115 touched experts of configuration 2),
     # scaled to this run's touched experts: the traffic is the weight stream, which grows in proportion
     traffic = None
     if wl.name == "c2":
-        traffic = 820.4e6 / 115.0 * statistics.mean(touched)
-    roof = {"kernel": "okc_grouped_gemm<0> (gate_up + SiLU*mul)", "bound": "hbm", "achieved": achieved, "peak": peak_gbs,
+        traffic = NCU_TRAFFIC_C2_115 / 115.0 * statistics.mean(touched)
+    roof = {"kernel": "okc_moe_gemm (gate_up + SiLU*mul units, then down units, one launch)", "bound": "hbm", "achieved": achieved, "peak": peak_gbs,
             "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": traffic,
             "kernel_ms": {k: statistics.mean(v) for k, v in phases.items()},
             "step_frac_of_peak": value / (peak_gbs * world)}

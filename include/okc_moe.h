@@ -1,9 +1,9 @@
 /*
  * okc_moe.h — C ABI of the B200 (sm_100a) NVFP4 W4A16 MoE decode step.
  *
- * Every entry point is `extern "C"`, takes plain pointers and sizes, allocates nothing,
- * keeps no process-global mutable state, enqueues its work on the given CUDA stream and
- * returns 0 or a negative okc_moe_error.  All device buffers are owned by the caller.
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, allocates no memory
+ * (okc_moe_experts_profiled alone creates and destroys CUDA events), enqueues its work on the
+ * given CUDA stream and returns 0 or a negative okc_moe_error.  All device buffers are owned by the caller.
  * Device-side waits are bounded; a wait that ran out is reported through the status
  * word (okc_moe_read_status), never by a trap.
  *
@@ -99,8 +99,9 @@ int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weig
                  int own_t0, int own_t1, void* workspace, okc_stream_t stream);
 
 /*
- * The experts on the routes sorted into `workspace`: gather -> gate_up GEMM + SiLU*mul ->
- * down GEMM (x routing weight, un-permuted) -> per-token combine.
+ * The experts on the routes sorted into `workspace`: gather -> one persistent launch of the
+ * gate_up GEMM + SiLU*mul units and the down GEMM (x routing weight, un-permuted) units, a down
+ * unit starting as soon as the gate_up units of its own work item are done -> per-token combine.
  * hidden: bf16 [T, H] with row stride `hidden_stride` elements.  gs13 / gs2: f32 [expert_slots].
  * post_norm_w: bf16 [H] or NULL.  out: bf16 [T, H] when out_f32 == 0, else f32 [T, H] (the
  * partial sum an expert-parallel reduce-scatter consumes).  Rows with no local route are zero.
@@ -111,9 +112,10 @@ int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void
                     int T, const void* post_norm_w, void* workspace, void* out, int out_f32,
                     okc_stream_t stream);
 
-/* okc_moe_experts with CUDA events around its four kernels: synchronises, then writes their
- * durations in milliseconds to the host array phase_ms[4] = {gather, gate_up, down, combine}.
- * A measurement aid (it creates and destroys five events); not for the serving path.  Plays the
+/* okc_moe_experts with CUDA events around its three kernels: synchronises, then writes their
+ * durations in milliseconds to the host array phase_ms[4] = {gather, grouped GEMMs (gate_up and
+ * down units in one launch), combine, whole call}.
+ * A measurement aid (it creates and destroys four events); not for the serving path.  Plays the
  * role of the reference's DIAG timing harness (submission.py:6151-6231). */
 int okc_moe_experts_profiled(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
                              const float* gs13, const float* gs2, const void* hidden,

@@ -44,8 +44,10 @@ static bool encode_rows_map(CUtensorMap* map, void* base, uint64_t rows, uint64_
 #ifdef OKC_WAIT_PROFILE
 static std::atomic<int> g_dbg_flags{0};
 #define OKC_DBG_FLAGS g_dbg_flags.load()
+#define OKC_DBG_SPLIT ((g_dbg_flags.load() >> 8) & 1)
 #else
 #define OKC_DBG_FLAGS 0
+#define OKC_DBG_SPLIT 0
 #endif
 
 static int ncap_for(int T) { return chunk_rows_for(T); }
@@ -70,6 +72,7 @@ struct Ws {
   int32_t* meta;
   int32_t* counts;
   int4* items;
+  int32_t* done;
   int32_t* sorted;
   int32_t* pos;
   float* wsorted;
@@ -84,6 +87,7 @@ static Ws carve(void* workspace, const Geometry& g) {
   w.meta = reinterpret_cast<int32_t*>(b + g.off_meta);
   w.counts = reinterpret_cast<int32_t*>(b + g.off_counts);
   w.items = reinterpret_cast<int4*>(b + g.off_items);
+  w.done = reinterpret_cast<int32_t*>(b + g.off_done);
   w.sorted = reinterpret_cast<int32_t*>(b + g.off_sorted);
   w.pos = reinterpret_cast<int32_t*>(b + g.off_pos);
   w.wsorted = reinterpret_cast<float*>(b + g.off_wsorted);
@@ -137,7 +141,7 @@ const char* okc_moe_strerror(int code) {
   }
 }
 
-int okc_moe_launches_per_step(void) { return 5; }
+int okc_moe_launches_per_step(void) { return 4; }
 
 int okc_moe_query(const okc_moe_plan* plan, okc_moe_sizes* out) {
   Geometry g;
@@ -224,38 +228,44 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   const int ncap = ncap_for(T);
 
   if (ev && cudaEventRecord(ev[0], stream) != cudaSuccess) return OKC_ERR_CUDA;
-  if (launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, w.done, g.max_items, stream) != cudaSuccess)
+    return OKC_ERR_CUDA;
   if (ev && cudaEventRecord(ev[1], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
-  GemmParams a;
+  // Both GEMM phases in one persistent launch: gate_up units first, then down units, each down
+  // unit waiting for the gate_up units of its own work item only.
+  MoeGemmParams a;
   memset(&a, 0, sizeof(a));
   const uint32_t boxes[2] = {16, 32};
-  for (int i = 0; i < 2; ++i)
-    if (!encode_rows_map(&a.bmap[i], w.xg, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.H), boxes[i])) return OKC_ERR_CUDA;
-  a.wpacked = static_cast<const uint8_t*>(packed_w13); a.gs = gs13; a.meta = w.meta; a.items = w.items;
-  a.pairs = g.pairs13; a.stages = g.stages13; a.expert_bytes = g.w13_expert_bytes;
+  for (int i = 0; i < 2; ++i) {
+    if (!encode_rows_map(&a.ph[0].bmap[i], w.xg, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.H), boxes[i])) return OKC_ERR_CUDA;
+    if (!encode_rows_map(&a.ph[1].bmap[i], w.inter, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.I), boxes[i])) return OKC_ERR_CUDA;
+  }
+  a.ph[0].wpacked = static_cast<const uint8_t*>(packed_w13); a.ph[0].gs = gs13;
+  a.ph[0].pairs = g.pairs13; a.ph[0].stages = g.stages13; a.ph[0].expert_bytes = g.w13_expert_bytes;
+  a.ph[1].wpacked = static_cast<const uint8_t*>(packed_w2); a.ph[1].gs = gs2;
+  a.ph[1].pairs = g.pairs2; a.ph[1].stages = g.stages2; a.ph[1].expert_bytes = g.w2_expert_bytes;
+  a.meta = w.meta; a.items = w.items; a.done = w.done;
   a.ncap = ncap; a.n_stages = gemm_stages_for(ncap);
-  a.inter = w.inter; a.I = g.I; a.H = g.H; a.y = w.y; a.dbg = OKC_DBG_FLAGS;
-  if (launch_gemm(0, a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  a.inter = w.inter; a.I = g.I; a.H = g.H; a.y = w.y; a.sorted = w.sorted; a.wsorted = w.wsorted;
+  a.weighted = plan->post_norm ? 0 : 1; a.dbg = OKC_DBG_FLAGS;
+  if (!OKC_DBG_SPLIT) {
+    a.phase_lo = 0; a.phase_hi = 1; a.work_counter = w.meta + kMetaWorkFused;
+    if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  } else {
+    // measurement only: one launch per phase
+    a.phase_lo = 0; a.phase_hi = 0; a.work_counter = w.meta + kMetaWorkPhase0;
+    if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+    a.phase_lo = 1; a.phase_hi = 1; a.work_counter = w.meta + kMetaWorkPhase1;
+    if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  }
   if (ev && cudaEventRecord(ev[2], stream) != cudaSuccess) return OKC_ERR_CUDA;
-
-  GemmParams b;
-  memset(&b, 0, sizeof(b));
-  for (int i = 0; i < 2; ++i)
-    if (!encode_rows_map(&b.bmap[i], w.inter, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.I), boxes[i])) return OKC_ERR_CUDA;
-  b.wpacked = static_cast<const uint8_t*>(packed_w2); b.gs = gs2; b.meta = w.meta; b.items = w.items;
-  b.pairs = g.pairs2; b.stages = g.stages2; b.expert_bytes = g.w2_expert_bytes;
-  b.ncap = ncap; b.n_stages = gemm_stages_for(ncap);
-  b.y = w.y; b.sorted = w.sorted; b.wsorted = w.wsorted; b.H = g.H; b.I = g.I;
-  b.weighted = plan->post_norm ? 0 : 1; b.dbg = OKC_DBG_FLAGS;
-  if (launch_gemm(1, b, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
-  if (ev && cudaEventRecord(ev[3], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
   CombineParams c;
   c.y = w.y; c.pos = w.pos; c.wsorted = w.wsorted; c.post_w = static_cast<const uint16_t*>(post_norm_w);
   c.out = out; c.kk = g.kk; c.H = g.H; c.out_f32 = out_f32 ? 1 : 0;
   if (launch_combine(c, T, stream) != cudaSuccess) return OKC_ERR_CUDA;
-  if (ev && cudaEventRecord(ev[4], stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (ev && cudaEventRecord(ev[3], stream) != cudaSuccess) return OKC_ERR_CUDA;
   return OKC_OK;
 }
 
@@ -272,18 +282,20 @@ int okc_moe_experts_profiled(const okc_moe_plan* plan, const void* packed_w13, c
                              float* phase_ms) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!phase_ms) return OKC_ERR_BAD_ARG;
-  cudaEvent_t ev[5];
+  cudaEvent_t ev[4];
   int made = 0;
   int rc = OKC_OK;
-  for (; made < 5; ++made)
+  for (; made < 4; ++made)
     if (cudaEventCreate(&ev[made]) != cudaSuccess) { rc = OKC_ERR_CUDA; break; }
   if (rc == OKC_OK)
     rc = experts_impl(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, T, post_norm_w, workspace, out,
                       out_f32, stream, ev);
-  if (rc == OKC_OK && cudaEventSynchronize(ev[4]) != cudaSuccess) rc = OKC_ERR_CUDA;
-  if (rc == OKC_OK)
-    for (int i = 0; i < 4; ++i)
+  if (rc == OKC_OK && cudaEventSynchronize(ev[3]) != cudaSuccess) rc = OKC_ERR_CUDA;
+  if (rc == OKC_OK) {
+    for (int i = 0; i < 3; ++i)
       if (cudaEventElapsedTime(&phase_ms[i], ev[i], ev[i + 1]) != cudaSuccess) rc = OKC_ERR_CUDA;
+    if (cudaEventElapsedTime(&phase_ms[3], ev[0], ev[3]) != cudaSuccess) rc = OKC_ERR_CUDA;
+  }
   for (int i = 0; i < made; ++i) cudaEventDestroy(ev[i]);
   return rc;
 }

@@ -28,7 +28,9 @@ constexpr uint32_t kOutMask = 0x81C081C0u;     // sign + 3 magnitude bits of bot
 constexpr uint32_t kLeftMask = 0x60306030u;    // bits of w0 its three rotations leave over
 
 // meta words at the start of the workspace
-enum MetaWord { kMetaItems = 0, kMetaLocalRoutes = 1, kMetaStatus = 2, kMetaDetail = 3, kMetaTokens = 4, kMetaWords = 64 };
+enum MetaWord { kMetaItems = 0, kMetaLocalRoutes = 1, kMetaStatus = 2, kMetaDetail = 3, kMetaTokens = 4,
+                kMetaWorkFused = 8, kMetaWorkPhase0 = 9, kMetaWorkPhase1 = 10,   // unit counters of the GEMM launches
+                kMetaWords = 64 };
 
 struct Geometry {
   int H, I, slots, kk, T, R, Rpad;
@@ -36,7 +38,7 @@ struct Geometry {
   size_t w13_expert_bytes, w2_expert_bytes;
   int max_items;
   // workspace byte offsets
-  size_t off_meta, off_counts, off_items, off_sorted, off_pos, off_wsorted, off_xg, off_inter, off_y, total;
+  size_t off_meta, off_counts, off_items, off_done, off_sorted, off_pos, off_wsorted, off_xg, off_inter, off_y, total;
 };
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -70,6 +72,7 @@ inline bool make_geometry(const okc_moe_plan& p, Geometry& g) {
   g.off_meta = o;     o = align_up(o + kMetaWords * 4, 256);
   g.off_counts = o;   o = align_up(o + static_cast<size_t>(g.slots + 1) * 4, 256);
   g.off_items = o;    o = align_up(o + static_cast<size_t>(g.max_items) * 16, 256);
+  g.off_done = o;     o = align_up(o + static_cast<size_t>(g.max_items) * 4, 256);
   g.off_sorted = o;   o = align_up(o + static_cast<size_t>(g.R) * 4, 256);
   g.off_pos = o;      o = align_up(o + static_cast<size_t>(g.R) * 4, 256);
   g.off_wsorted = o;  o = align_up(o + static_cast<size_t>(g.R) * 4, 256);

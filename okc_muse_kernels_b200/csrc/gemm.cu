@@ -45,8 +45,9 @@ constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 6;
 
 // Codes written to the status word when a wait gives up: role * 16 + barrier kind.
-enum WaitCode { kWaitProducerEmpty = 0x11, kWaitMmaAccEmpty = 0x21, kWaitMmaFull = 0x22, kWaitMmaAFull = 0x23,
-                kWaitDqFull = 0x31, kWaitDqAEmpty = 0x32, kWaitEpiAccFull = 0x41 };
+enum WaitCode { kWaitProducerEmpty = 0x11, kWaitProducerUnit = 0x12, kWaitProducerDone = 0x13,
+                kWaitMmaAccEmpty = 0x21, kWaitMmaFull = 0x22, kWaitMmaAFull = 0x23, kWaitMmaUnit = 0x24,
+                kWaitDqFull = 0x31, kWaitDqAEmpty = 0x32, kWaitDqUnit = 0x33, kWaitEpiAccFull = 0x41, kWaitEpiUnit = 0x42 };
 
 
 // Optional wait profile (compile with -DOKC_WAIT_PROFILE): per CTA, cycles each role spent in
@@ -55,12 +56,12 @@ enum WaitCode { kWaitProducerEmpty = 0x11, kWaitMmaAccEmpty = 0x21, kWaitMmaFull
 #ifdef OKC_WAIT_PROFILE
 constexpr int kProfCtas = 256;
 constexpr int kProfSlots = 16;
-__device__ long long g_wait_prof[2][kProfCtas][kProfSlots];
+__device__ long long g_wait_prof[kProfCtas][kProfSlots];
 #define OKC_PROF_DECL long long prof_acc[kProfSlots] = {0}; const long long prof_t0 = clock64();
 #define OKC_PROF_WAIT(idx, expr) ([&] { const long long _t = clock64(); const bool _r = (expr); prof_acc[idx] += clock64() - _t; return _r; }())
 #define OKC_PROF_VOID(idx, stmt) { const long long _t = clock64(); stmt; prof_acc[idx] += clock64() - _t; }
 #define OKC_DBG(bit) ((p.dbg >> (bit)) & 1)
-#define OKC_PROF_STORE(idx_total, lo, hi) { prof_acc[idx_total] = clock64() - prof_t0; if (blockIdx.x < kProfCtas) for (int _i = lo; _i <= hi; ++_i) g_wait_prof[MODE][blockIdx.x][_i] = prof_acc[_i]; }
+#define OKC_PROF_STORE(idx_total, lo, hi) { prof_acc[idx_total] = clock64() - prof_t0; if (blockIdx.x < kProfCtas) for (int _i = lo; _i <= hi; ++_i) g_wait_prof[blockIdx.x][_i] = prof_acc[_i]; }
 #else
 #define OKC_DBG(bit) 0
 #define OKC_PROF_DECL
@@ -69,6 +70,21 @@ __device__ long long g_wait_prof[2][kProfCtas][kProfSlots];
 #define OKC_PROF_STORE(idx_total, lo, hi)
 #endif
 
+constexpr int kURing = 4;             // units the producer may run ahead of the other roles
+constexpr int kUnitConsumers = kIssuers + kDequantWarps + 4;   // warps that read every unit descriptor
+
+// A unit of work as the producer publishes it to the other roles of the CTA.
+struct UnitDesc {
+  int phase;      // 0 gate_up, 1 down; -1 = no more units
+  int slot;       // expert slot (weights, global scale)
+  int pos0;       // first row of the item in the sorted route order
+  int rows;       // token rows of the item
+  int npad;       // rows padded to 16 or 32 (N of the MMAs)
+  int pair;       // tile pair within the expert
+  int item;       // work item index
+  int stages;     // K / 256 of this phase
+};
+
 struct Ctrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -76,13 +92,29 @@ struct Ctrl {
   uint64_t a_empty[2 * kASlots];    // [slot][tile]: that tile's MMAs on the slot completed
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t u_full[kURing];          // unit descriptor published
+  uint64_t u_empty[kURing];         // every consumer warp has read it
   uint64_t dummy;                   // arrived on, never waited on
+  UnitDesc units[kURing];
   uint32_t tmem_base;
   int abort_code;
 };
 
-template <int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid_constant__ GemmParams p) {
+// Next unit descriptor for a consumer role: waits until the producer published ring entry
+// (n mod kURing), copies it, and frees the entry for this warp.  kWholeWarp: all 32 lanes call it
+// (lane 0 frees the entry once every lane has its copy); otherwise one lane alone does.
+template <bool kWholeWarp>
+__device__ __forceinline__ bool next_unit(Ctrl* ctrl, uint32_t bar_ufull, uint32_t bar_uempty, uint32_t n, bool lane0,
+                                          volatile int* abort_flag, int code, UnitDesc& u) {
+  const uint32_t k = n % kURing;
+  if (!mbar_wait(bar_ufull + 8 * k, (n / kURing) & 1, abort_flag, code)) return false;
+  u = ctrl->units[k];
+  if (kWholeWarp) __syncwarp();
+  mbar_arrive_if(bar_uempty + 8 * k, lane0);
+  return u.phase >= 0;
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_constant__ MoeGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem0 - smem_u32(smem_raw));
@@ -94,6 +126,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   // the warp index through a shuffle: the compiler then knows it is the same in every lane and keeps
   // what is derived from it (roles, barrier addresses, TMEM columns) in uniform registers
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const bool lane0 = lane == 0;
   const int NS = p.n_stages;
   // accumulators in TMEM columns [256, 512): per buffer eight blocks of ncap columns,
   // block (tile * 4 + K block of the stage); ncap is 16 (two buffers) or 32 (one)
@@ -103,6 +136,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   const uint32_t bar_full = smem_u32(&ctrl->full[0]), bar_empty = smem_u32(&ctrl->empty[0]);
   const uint32_t bar_afull = smem_u32(&ctrl->a_full[0]), bar_aempty = smem_u32(&ctrl->a_empty[0]);
   const uint32_t bar_accfull = smem_u32(&ctrl->acc_full[0]), bar_accempty = smem_u32(&ctrl->acc_empty[0]);
+  const uint32_t bar_ufull = smem_u32(&ctrl->u_full[0]), bar_uempty = smem_u32(&ctrl->u_empty[0]);
 
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
@@ -116,6 +150,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_accfull + 8 * i, kIssuers);
       mbar_init(bar_accempty + 8 * i, 4);
+    }
+    for (int i = 0; i < kURing; ++i) {
+      mbar_init(bar_ufull + 8 * i, 1);
+      mbar_init(bar_uempty + 8 * i, kUnitConsumers);
     }
     mbar_init(smem_u32(&ctrl->dummy), 1);
     ctrl->abort_code = 0;
@@ -133,35 +171,69 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   // everything above overlapped the tail of the kernel before; its outputs are read from here on
   griddep_wait();
   griddep_launch_dependents();
-  const int n_items = p.meta[kMetaItems];
-  const int total_units = n_items * p.pairs;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      for (int i = 0; i < 2; ++i) tma_prefetch_desc(&p.bmap[i]);
+      for (int ph = 0; ph < 2; ++ph)
+        for (int i = 0; i < 2; ++i) tma_prefetch_desc(&p.ph[ph].bmap[i]);
       const uint64_t pol = policy_evict_first();
+      const int n_items = p.meta[kMetaItems];
+      const int units0 = n_items * p.ph[0].pairs, units1 = n_items * p.ph[1].pairs;
+      const int first = (p.phase_lo == 0) ? 0 : units0;
+      const int last = (p.phase_hi == 1) ? units0 + units1 : units0;
       int st = 0;
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
       OKC_PROF_DECL
-      for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
-        const int item = u / p.pairs, pair = u - item * p.pairs;
-        const int4 wi = p.items[item];
-        const int npad = wi.w;
-        const int mi = (npad == 16) ? 0 : 1;
-        const uint8_t* src = p.wpacked + static_cast<size_t>(wi.x) * p.expert_bytes +
-                             static_cast<size_t>(pair) * p.stages * kStageBytes;
-        for (int s = 0; s < p.stages; ++s) {
+      for (uint32_t n = 0; ok; ++n) {
+        const uint32_t k = n % kURing;
+        if (!mbar_wait<200>(bar_uempty + 8 * k, ((n / kURing) & 1) ^ 1, abort_flag, kWaitProducerUnit)) { ok = false; break; }
+        const int g = first + atomicAdd(p.work_counter, 1);
+        UnitDesc u;
+        if (g >= last) {
+          u.phase = -1; u.slot = 0; u.pos0 = 0; u.rows = 0; u.npad = 16; u.pair = 0; u.item = 0; u.stages = 0;
+          ctrl->units[k] = u;
+          mbar_arrive(bar_ufull + 8 * k);
+          break;
+        }
+        u.phase = (g < units0) ? 0 : 1;
+        const PhaseParams& pp = p.ph[u.phase];
+        const int gl = (u.phase == 0) ? g : g - units0;
+        u.item = gl / pp.pairs;
+        u.pair = gl - u.item * pp.pairs;
+        const int4 wi = p.items[u.item];
+        u.slot = wi.x; u.pos0 = wi.y; u.rows = wi.z; u.npad = wi.w; u.stages = pp.stages;
+        ctrl->units[k] = u;
+        mbar_arrive(bar_ufull + 8 * k);
+        if (u.phase == 1) {
+          // the token operand of a down unit is the gate_up output of its work item: wait until the
+          // four epilogue warps of each of the item's gate_up units have stored and published it
+          const int target = 4 * p.ph[0].pairs;
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(p.done + u.item) < target) {
+            __nanosleep(100);
+            if ((++spins & 255u) == 0) {
+              if (*abort_flag != 0) { ok = false; break; }
+              if (spins >= (1u << 22)) { atomicCAS(const_cast<int*>(abort_flag), 0, kWaitProducerDone); ok = false; break; }
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async();   // those stores were generic-proxy writes; the loads below are TMA
+        }
+        const int mi = (u.npad == 16) ? 0 : 1;
+        const uint8_t* src = pp.wpacked + static_cast<size_t>(u.slot) * pp.expert_bytes +
+                             static_cast<size_t>(u.pair) * pp.stages * kStageBytes;
+        for (int s = 0; s < pp.stages; ++s) {
           if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
           const uint32_t bar = bar_full + 8 * st;
           const uint32_t dst = smem0 + st * stage_bytes;
-          mbar_expect_tx(bar, kStageBytes + npad * 512);
+          mbar_expect_tx(bar, kStageBytes + u.npad * 512);
           bulk_g2s_hint(dst, src + static_cast<size_t>(s) * kStageBytes, kStageBytes, bar, pol);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
-            tma_2d_g2s(dst + kStageBytes + kb * npad * 128, &p.bmap[mi], s * kStageK + kb * 64, wi.y, bar);
+            tma_2d_g2s(dst + kStageBytes + kb * u.npad * 128, &pp.bmap[mi], s * kStageK + kb * 64, u.pos0, bar);
           ++issued;
           if (++st == NS) { st = 0; ph ^= 1; }
         }
@@ -184,26 +256,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
       const int tile = warp & 1, kb = warp >> 1;
       const uint32_t my_afull = bar_afull + 16 * kb + 8 * tile, my_aempty = bar_aempty + 16 * kb + 8 * tile;
       const uint32_t a0 = tmem + kb * kASlotCols + tile * 32;
-      int st = 0, unit_it = 0;
+      int st = 0;
       uint32_t ph = 0, sph = 0;     // stage ring phase; A-slot phase (flips once per stage)
-      bool ok = true;
       OKC_PROF_DECL
       const uint32_t desc_hi = static_cast<uint32_t>(smem_desc_sw128(0) >> 32);
       const uint32_t desc_lo_const = static_cast<uint32_t>(smem_desc_sw128(0));
-      for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x, ++unit_it) {
-        const int item = u / p.pairs;
-        const uint32_t npad = static_cast<uint32_t>(p.items[item].w);
+      UnitDesc u;
+      for (uint32_t unit_it = 0; next_unit<false>(ctrl, bar_ufull, bar_uempty, unit_it, true, abort_flag, kWaitMmaUnit, u); ++unit_it) {
+        const uint32_t npad = static_cast<uint32_t>(u.npad);
         const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
-        if (!OKC_PROF_WAIT(2, mbar_wait<500>(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) { ok = false; break; }
+        if (!OKC_PROF_WAIT(2, mbar_wait<500>(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) goto issuer_done;
         tc_fence_after();
         const uint32_t idesc = idesc_bf16_m128(npad);
         const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + (tile * 4 + kb) * p.ncap;
         const uint32_t kb_off = kb * ((npad * 128u) >> 4);   // descriptor units to this issuer's K block
         uint32_t acc = 0;
-        for (int s = 0; s < p.stages; ++s) {
-          if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) { ok = false; break; }
+        for (int s = 0; s < u.stages; ++s) {
+          if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) goto issuer_done;
           const uint32_t lo = (desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4)) + kb_off;
-          if (!OKC_PROF_WAIT(4, mbar_wait(my_afull, sph, abort_flag, kWaitMmaAFull))) { ok = false; break; }
+          if (!OKC_PROF_WAIT(4, mbar_wait(my_afull, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
           tc_fence_after();
           if (!OKC_DBG(1)) {
             mma_ts2(d, a0, lo, desc_hi, idesc, acc);
@@ -217,8 +288,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
           sph ^= 1;
           if (++st == NS) { st = 0; ph ^= 1; }
         }
-        if (ok) mma_commit(bar_accfull + 8 * buf);
+        mma_commit(bar_accfull + 8 * buf);
       }
+    issuer_done:
       if (warp == 0) { OKC_PROF_STORE(5, 2, 5) }
     }
   } else if (warp >= kDequantWarp0 && warp < kDequantWarp0 + kDequantWarps) {
@@ -234,68 +306,75 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
     const uint32_t code_off = tile * kTileBytes + row * 16;
     const uint32_t scale_off = tile * kTileBytes + kTileCodeBytes + row * 2;
     const uint32_t my_afull = bar_afull + 8 * tile, my_aempty = bar_aempty + 8 * tile;
-    const bool lane0 = lane == 0;
-    // this role only counts stages: units handled by this CTA x stages per unit
-    const int my_units = (static_cast<int>(blockIdx.x) < total_units)
-                             ? (total_units - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
-                             : 0;
-    const int total_stages = my_units * p.stages;
     int st = 0;
     // barrier of the A slot stored to but not yet handed over; a barrier nobody waits on stands in
     // before the first slot, so the hand-over below needs no "is anything pending" test
     uint32_t pend_bar = smem_u32(&ctrl->dummy);
     uint32_t ph = 0, sph = 0;
     OKC_PROF_DECL
-    for (int it = 0; it < total_stages; ++it) {
-      if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) goto dq_done;
-      {
-        const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
-        const uint32_t simg = smem0 + st * stage_bytes + scale_off;
+    UnitDesc u;
+    for (uint32_t unit_it = 0; next_unit<true>(ctrl, bar_ufull, bar_uempty, unit_it, lane0, abort_flag, kWaitDqUnit, u); ++unit_it) {
+      for (int s = 0; s < u.stages; ++s) {
+        if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) goto dq_done;
+        {
+          const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
+          const uint32_t simg = smem0 + st * stage_bytes + scale_off;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int kb = grp + 2 * h;
-          // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
-          const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb) * (kTileRows * 16));
-          const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb + 1) * (kTileRows * 16));
-          const uint32_t sp0 = simg + (2 * kb) * (kTileRows * 2);
-          const uint32_t sp1 = sp0 + kTileRows * 2;
-          const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
-          uint32_t r[16];
-          if (!OKC_DBG(0)) {
-            dequant_chunk(w0, s00, s01, r);
-          } else {
+          for (int h = 0; h < 2; ++h) {
+            const int kb = grp + 2 * h;
+            // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
+            const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb) * (kTileRows * 16));
+            const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb + 1) * (kTileRows * 16));
+            const uint32_t sp0 = simg + (2 * kb) * (kTileRows * 2);
+            const uint32_t sp1 = sp0 + kTileRows * 2;
+            const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
+            uint32_t r[16];
+            if (!OKC_DBG(0)) {
+              dequant_chunk(w0, s00, s01, r);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = w0.x ^ s00;
-          }
-          // the stores of the previous slot completed while this chunk was being dequantised:
-          // only now wait for them and hand that slot to its MMA issuer
-          OKC_PROF_VOID(8, tmem_wait_st())
-          tc_fence_before();
-          mbar_arrive_if(pend_bar, lane0);
-          // every lane polls the same barrier in the same instruction, so the outcome is the same
-          // in all of them and the warp stays converged for the tensor-memory stores below
-          if (!OKC_PROF_WAIT(7, mbar_wait(my_aempty + 16 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) goto dq_done;
-          tc_fence_after();
-          if (!OKC_DBG(2)) tmem_st16(trow + kb * kASlotCols, r);
-          if (!OKC_DBG(0)) {
-            dequant_chunk(w1, s10, s11, r);
-          } else {
+              for (int i = 0; i < 16; ++i) r[i] = w0.x ^ s00;
+            }
+            // the stores of the previous slot completed while this chunk was being dequantised:
+            // only now wait for them and hand that slot to its MMA issuer
+            OKC_PROF_VOID(8, tmem_wait_st())
+            tc_fence_before();
+            mbar_arrive_if(pend_bar, lane0);
+            // every lane polls the same barrier in the same instruction, so the outcome is the same
+            // in all of them and the warp stays converged for the tensor-memory stores below
+            if (!OKC_PROF_WAIT(7, mbar_wait(my_aempty + 16 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) goto dq_done;
+            tc_fence_after();
+            if (!OKC_DBG(2)) tmem_st16(trow + kb * kASlotCols, r);
+            if (!OKC_DBG(0)) {
+              dequant_chunk(w1, s10, s11, r);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = w1.y ^ s10;
+              for (int i = 0; i < 16; ++i) r[i] = w1.y ^ s10;
+            }
+            if (!OKC_DBG(2)) {
+              tmem_st16(trow + kb * kASlotCols + 16, r);
+            } else if (r[3] == 0x12345678u) {
+              p.y[0] = 1.0f;   // keeps the registers alive
+            }
+            pend_bar = my_afull + 16 * kb;
           }
-          if (!OKC_DBG(2)) {
-            tmem_st16(trow + kb * kASlotCols + 16, r);
-          } else if (r[3] == 0x12345678u) {
-            p.y[0] = 1.0f;   // keeps the registers alive
-          }
-          pend_bar = my_afull + 16 * kb;
         }
+        // the stage's bytes have been consumed (the loads fed the arithmetic above): hand the
+        // shared-memory slot back
+        mbar_arrive_if(bar_empty + 8 * st, lane0);
+        sph ^= 1;
+        if (++st == NS) { st = 0; ph ^= 1; }
       }
-      // the stage's bytes have been consumed (the loads fed the arithmetic above): hand the
-      // shared-memory slot back
-      mbar_arrive_if(bar_empty + 8 * st, lane0);
-      sph ^= 1;
-      if (++st == NS) { st = 0; ph ^= 1; }
+      // The unit's last slot is normally handed over while the first chunk of the next unit is
+      // being dequantised.  If that chunk has not arrived, hand the slot over now: the producer may
+      // be holding the next unit back until another CTA's -- or this CTA's -- gate_up epilogue has
+      // run, and this unit's epilogue cannot run before its last MMAs have their operand.
+      if (!__all_sync(0xffffffffu, mbar_test(bar_full + 8 * st, ph))) {
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive_if(pend_bar, lane0);
+        pend_bar = smem_u32(&ctrl->dummy);
+      }
     }
   dq_done:
     tmem_wait_st();
@@ -304,24 +383,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
 #ifdef OKC_WAIT_PROFILE
     if (lane == 0 && blockIdx.x < kProfCtas && (warp == kDequantWarp0 || warp == kDequantWarp0 + kDequantWarps - 1)) {
       const int base = (warp == kDequantWarp0) ? 6 : 10;   // first and last dequantiser warp
-      for (int i = 0; i < 3; ++i) g_wait_prof[MODE][blockIdx.x][base + i] = prof_acc[6 + i];
-      g_wait_prof[MODE][blockIdx.x][base + 3] = clock64() - prof_t0;
+      for (int i = 0; i < 3; ++i) g_wait_prof[blockIdx.x][base + i] = prof_acc[6 + i];
+      g_wait_prof[blockIdx.x][base + 3] = clock64() - prof_t0;
     }
 #endif
-  } else if (warp >= kEpilogueWarp0) {
+  } else if (warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + 4) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
-    int unit_it = 0;
-    bool ok = true;
-    for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x, ++unit_it) {
-      const int item = u / p.pairs, pair = u - item * p.pairs;
-      const int4 wi = p.items[item];
-      const int n_rows = wi.z, npad = wi.w;
+    UnitDesc u;
+    for (uint32_t unit_it = 0; next_unit<true>(ctrl, bar_ufull, bar_uempty, unit_it, lane0, abort_flag, kWaitEpiUnit, u); ++unit_it) {
+      const int n_rows = u.rows, npad = u.npad;
       const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
-      const float sc = p.gs[wi.x] * 256.0f;
-      if (!mbar_wait<2000>(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) { ok = false; break; }
+      const float sc = p.ph[u.phase].gs[u.slot] * 256.0f;
+      if (!mbar_wait<2000>(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) break;
       tc_fence_after();
       const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * acc_buf_stride;     // tile 0, K block 0
       const uint32_t d1 = d0 + 4 * p.ncap;                                        // tile 1, K block 0
@@ -347,8 +423,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
         if (c0 + 16 >= npad) {
           // last read of this accumulator: the MMA warps may overwrite it
           tc_fence_before();
-          __syncwarp();
-          mbar_arrive_if(bar_accempty + 8 * buf, lane == 0);
+          mbar_arrive_if(bar_accempty + 8 * buf, lane0);
         }
         if (c0 < n_rows) {
 #pragma unroll
@@ -357,19 +432,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
             if (n < n_rows) {
               const float va = __uint_as_float(a[j]) * sc;
               const float vb = __uint_as_float(b[j]) * sc;
-              if (MODE == 0) {
+              if (u.phase == 0) {
                 const float act = va / (1.0f + __expf(-va)) * vb;
-                p.inter[static_cast<size_t>(wi.y + n) * p.I + pair * kTileRows + row] =
+                p.inter[static_cast<size_t>(u.pos0 + n) * p.I + u.pair * kTileRows + row] =
                     __bfloat16_as_ushort(__float2bfloat16_rn(act));
               } else {
-                const int route = p.sorted[wi.y + n];
-                const float wgt = p.weighted ? p.wsorted[wi.y + n] : 1.0f;
-                float* dst = p.y + static_cast<size_t>(route) * p.H + pair * 2 * kTileRows + row;
+                const int route = p.sorted[u.pos0 + n];
+                const float wgt = p.weighted ? p.wsorted[u.pos0 + n] : 1.0f;
+                float* dst = p.y + static_cast<size_t>(route) * p.H + u.pair * 2 * kTileRows + row;
                 dst[0] = va * wgt;
                 dst[kTileRows] = vb * wgt;
               }
             }
           }
+        }
+      }
+      if (u.phase == 0) {
+        // publish this warp's part of the gate_up output to the producers (of any CTA) that will
+        // stream it as the token operand of the item's down units through TMA
+        __threadfence();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane0) {
+          __threadfence();
+          atomicAdd(p.done + u.item, 1);
         }
       }
     }
@@ -384,7 +470,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_grouped_gemm(const __grid
   }
   if (tid == 0 && ctrl->abort_code != 0) {
     atomicCAS(const_cast<int32_t*>(&p.meta[kMetaStatus]), 0, OKC_ERR_TIMEOUT);
-    atomicCAS(const_cast<int32_t*>(&p.meta[kMetaDetail]), 0, (MODE << 8) | ctrl->abort_code);
+    atomicCAS(const_cast<int32_t*>(&p.meta[kMetaDetail]), 0, ((p.phase_lo * 2 + p.phase_hi) << 8) | ctrl->abort_code);
   }
 }
 
@@ -492,7 +578,7 @@ cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t
 }
 
 #ifdef OKC_WAIT_PROFILE
-// host_out: long long [2][256][16] = per kernel (gate_up, down), per CTA:
+// host_out: long long [256][16] = per CTA of the last launch:
 // 0 producer total, 1 producer wait-empty, 2 mma wait acc-empty, 3 mma wait full, 4 mma wait a-full, 5 mma total,
 // 6..9 first dequantiser warp: wait full, wait a-empty, wait tcgen05.st, total; 10..13 the same for the last one.
 extern "C" int okc_moe_debug_wait_profile(long long* host_out) {
@@ -511,21 +597,11 @@ int gemm_stages_for(int ncap) {
   return n > kMaxStages ? kMaxStages : n;
 }
 
-cudaError_t launch_gemm(int mode, const GemmParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream) {
   const size_t smem = gemm_smem_bytes(p.n_stages, p.ncap);
-  cudaError_t e;
-  if (mode == 0) {
-    e = cudaFuncSetAttribute(okc_grouped_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-    e = launch_kernel(okc_grouped_gemm<0>, dim3(grid), dim3(kGemmThreads), smem, stream, true, p);
-    if (e != cudaSuccess) return e;
-  } else {
-    e = cudaFuncSetAttribute(okc_grouped_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-    e = launch_kernel(okc_grouped_gemm<1>, dim3(grid), dim3(kGemmThreads), smem, stream, true, p);
-    if (e != cudaSuccess) return e;
-  }
-  return cudaGetLastError();
+  cudaError_t e = cudaFuncSetAttribute(okc_moe_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  return launch_kernel(okc_moe_gemm, dim3(grid), dim3(kGemmThreads), smem, stream, true, p);
 }
 
 // The combine without the post-expert norm needs no row-wide reduction, so a token's row is cut

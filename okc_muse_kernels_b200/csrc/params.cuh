@@ -21,8 +21,8 @@ struct RouteParams {
   int T, E, k, kk, slots, local_start, local_count, has_shared, own_t0, own_t1, max_items, chunk_rows;
 };
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
-cudaError_t launch_gather(const void* hidden, int64_t stride, const int32_t* meta, const int32_t* sorted, int kk,
-                          int H, int R, void* xg, cudaStream_t stream);
+cudaError_t launch_gather(const void* hidden, int64_t stride, int32_t* meta, const int32_t* sorted, int kk,
+                          int H, int R, void* xg, int32_t* done, int max_items, cudaStream_t stream);
 
 struct RepackParams {
   const uint8_t* w;
@@ -39,27 +39,38 @@ struct UnpackParams {
 };
 cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t stream);
 
-struct GemmParams {
-  CUtensorMap bmap[2];      // token operand [rows, K] bf16, box = 64 elements x {16, 32} rows
-  const uint8_t* wpacked;
-  const float* gs;
+// One of the two GEMM phases of a step: 0 = gate_up on w13 (token operand xg), 1 = down on w2
+// (token operand inter).
+struct PhaseParams {
+  CUtensorMap bmap[2];        // token operand [rows, K] bf16, box = 64 elements x {16, 32} rows
+  const uint8_t* wpacked;     // stage images of every expert slot
+  const float* gs;            // [slots] global scales
+  int pairs;                  // units per work item
+  int stages;                 // K / 256
+  size_t expert_bytes;
+};
+
+// The grouped-GEMM kernel works through the units of phases [phase_lo, phase_hi]: both phases in one
+// launch (gate_up units first, then down units, handed out by an atomic counter) or one phase.
+struct MoeGemmParams {
+  PhaseParams ph[2];
   const int32_t* meta;
   const int4* items;
-  int pairs;
-  int stages;
-  size_t expert_bytes;
-  int n_stages;
-  int ncap;
-  uint16_t* inter;
+  int32_t* work_counter;      // next unit of this launch (zeroed by the gather kernel)
+  int32_t* done;              // [items] epilogue warps that finished a gate_up unit of the item
+  int phase_lo, phase_hi;
+  int n_stages;               // shared-memory ring depth
+  int ncap;                   // largest padded token count (sizes the B part of a stage)
+  uint16_t* inter;            // bf16 [Rpad, I]     (phase 0 output, phase 1 token operand)
   int I;
-  float* y;
+  float* y;                   // f32 [R, H]         (phase 1 output)
   const int32_t* sorted;
   const float* wsorted;
   int H;
   int weighted;
   int dbg;   // experiment switches, honoured only by the -DOKC_WAIT_PROFILE build (0 otherwise)
 };
-cudaError_t launch_gemm(int mode, const GemmParams& p, int grid, cudaStream_t stream);
+cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream);
 int gemm_stages_for(int ncap);
 
 struct CombineParams {

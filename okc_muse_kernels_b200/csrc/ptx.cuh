@@ -58,6 +58,18 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 
 // Bounded wait.  Returns false when the phase did not complete within the retry limit or when
 // another role of the CTA already gave up (`*abort_flag` != 0); in the first case it records
@@ -213,6 +225,17 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 // kernel does before the wait (barrier set-up, TMEM allocation) overlaps the predecessor's tail.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------- cross-CTA publication
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Orders accesses made through the generic proxy (ordinary loads / stores) with accesses made
+// through the async proxy (TMA): needed on both sides when one CTA stores data with ordinary
+// stores that another CTA then fetches with a TMA load.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // ---------------------------------------------------------------- small math
 __device__ __forceinline__ uint32_t rotr32(uint32_t x, int s) { return __funnelshift_r(x, x, s); }

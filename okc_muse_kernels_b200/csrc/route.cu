@@ -218,13 +218,20 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
 }
 
 // xg[pos] = hidden[token of the route at pos]: rows of the gate_up GEMM's token operand in expert order.
+// Block 0 also clears the per-call state of the GEMM launches that follow: their unit counters and
+// the per-item completion counts.
 __global__ void __launch_bounds__(128) okc_gather_rows(const uint16_t* __restrict__ hidden, int64_t stride,
-                                                       const int32_t* __restrict__ meta,
+                                                       int32_t* __restrict__ meta,
                                                        const int32_t* __restrict__ sorted, int kk, int H,
-                                                       uint16_t* __restrict__ xg) {
+                                                       uint16_t* __restrict__ xg, int32_t* __restrict__ done,
+                                                       int max_items) {
   griddep_wait();   // the sort tables come from the kernel before
   griddep_launch_dependents();
   const int q = blockIdx.x;
+  if (q == 0) {
+    for (int i = threadIdx.x; i < max_items; i += blockDim.x) done[i] = 0;
+    if (threadIdx.x < 3) meta[kMetaWorkFused + threadIdx.x] = 0;
+  }
   if (q >= meta[kMetaLocalRoutes]) return;
   const int t = sorted[q] / kk;
   const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * stride);
@@ -269,10 +276,10 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_gather(const void* hidden, int64_t stride, const int32_t* meta, const int32_t* sorted, int kk,
-                          int H, int R, void* xg, cudaStream_t stream) {
+cudaError_t launch_gather(const void* hidden, int64_t stride, int32_t* meta, const int32_t* sorted, int kk,
+                          int H, int R, void* xg, int32_t* done, int max_items, cudaStream_t stream) {
   return launch_kernel(okc_gather_rows, dim3(R), dim3(128), 0, stream, true, static_cast<const uint16_t*>(hidden),
-                       stride, meta, sorted, kk, H, static_cast<uint16_t*>(xg));
+                       stride, meta, sorted, kk, H, static_cast<uint16_t*>(xg), done, max_items);
 }
 
 }  // namespace okc

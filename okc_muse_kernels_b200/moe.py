@@ -237,8 +237,9 @@ def moe_step(hidden_states: torch.Tensor, router_logits: torch.Tensor, state: di
 
 def experts_profiled(hidden_states: torch.Tensor, state: dict, out: torch.Tensor) -> dict:
     """The expert phase of a step whose routes are already sorted into the state (``route`` was
-    called), with CUDA events around its four kernels.  Synchronises; returns their durations in
-    milliseconds.  A measurement aid, not the serving path."""
+    called), with CUDA events around its three kernels.  Synchronises; returns their durations in
+    milliseconds (``gemm`` is the one launch that runs both grouped GEMMs) and the whole call's.
+    A measurement aid, not the serving path."""
     plan: MoEPlan = state["plan"]
     hidden, stride = _check_hidden(hidden_states, plan)
     ms = (C.c_float * 4)()
@@ -247,7 +248,7 @@ def experts_profiled(hidden_states: torch.Tensor, state: dict, out: torch.Tensor
         state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, hidden.shape[0],
         _ptr(state["post_norm_w"]), state["workspace"].data_ptr(), out.data_ptr(),
         int(out.dtype == torch.float32), _stream(), ms), "okc_moe_experts_profiled")
-    return {"gather": ms[0], "gate_up": ms[1], "down": ms[2], "combine": ms[3]}
+    return {"gather": ms[0], "gemm": ms[1], "combine": ms[2], "total": ms[3]}
 
 
 def cast_bf16(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
