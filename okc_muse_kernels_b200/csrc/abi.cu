@@ -120,7 +120,7 @@ using namespace okc;
 
 extern "C" {
 
-int okc_moe_version(void) { return 100; }
+int okc_moe_version(void) { return 101; }
 
 #ifdef OKC_WAIT_PROFILE
 // Experiment switches of the instrumented build: bit 0 skip the dequantisation arithmetic, bit 1 skip

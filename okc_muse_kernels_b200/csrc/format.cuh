@@ -84,17 +84,33 @@ inline bool make_geometry(const okc_moe_plan& p, Geometry& g) {
 }
 
 #ifdef __CUDACC__
-// One E4M3 scale byte -> bf16x2 {scale, scale} * 2^118.
-// byte << 4 is the bf16 whose value is e4m3 * 2^-120 (normal and subnormal codes alike); the
-// multiply by 0x00100010 puts it into both halves (an integer multiply: it runs on the FMA pipe,
-// which has room, rather than on the integer pipe the mask / rotate work saturates).  Two exact
-// bf16 multiplies bring it to e4m3 * 2^118 (<= 448 * 2^118, finite in bf16).
-__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t byte) {
-  uint32_t s = byte * 0x00100010u;
-  s = mul_bf16x2(s, 0x7F007F00u);      // * 2^127
-  return mul_bf16x2(s, 0x77007700u);   // * 2^111
+// One stored scale byte -> bf16x2 {scale, scale} * 2^118, with one integer multiply-add (issued to
+// the FMA pipe, which has room; the mask / rotate work saturates the integer pipe).
+// The stage image does not keep the E4M3 byte itself but `scale_code` of it (below): 16 + 8 * (E + 7)
+// + m for the value 2^E * (1 + m/8), with the E4M3 subnormals normalised.  Shifted left by 4 that is
+// the exponent and top mantissa bits of a bf16; the added constant rebiases the exponent by 2^118
+// (<= 448 * 2^118, finite in bf16).
+__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t stored) {
+  uint32_t d;
+  asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(stored), "n"(0x00100010u), "n"(0x76007600u));
+  return d;
+}
+#endif
+
+// E4M3 magnitude bits (0..127) of a block scale -> the byte kept in the stage image.
+//   normal (b >= 8):      value 2^(b/8 - 7) * (1 + (b%8)/8)        -> b + 16
+//   subnormal (b = 1..7): value b * 2^-9 = 2^E * (1 + m/8)         -> 16 + 8 * (E + 7) + m  (0, 8, 12, 16, 18, 20, 22)
+//   NaN (0x7F):           a byte whose bf16 is a NaN                -> 153
+//   zero:                 the repack clears the block's codes instead; any finite scale will do -> 16
+__host__ __device__ inline uint32_t scale_code(uint32_t b) {
+  if (b == 0x7Fu) return 153u;
+  if (b >= 8u) return b + 16u;
+  // b:        0   1  2   3   4   5   6   7
+  // code:    16   0  8  12  16  18  20  22
+  return (0x161412100C080010ull >> (8u * b)) & 0xFFu;
 }
 
+#ifdef __CUDACC__
 // x << k written as a multiply so that it is issued to the FMA pipe.
 template <int K>
 __device__ __forceinline__ uint32_t shl_mul(uint32_t x) {

@@ -71,30 +71,28 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the phase did not complete within the retry limit or when
-// another role of the CTA already gave up (`*abort_flag` != 0); in the first case it records
-// `code` in `*abort_flag` so that every other role leaves its own waits too.  The retry loop is
-// kept to a handful of instructions because retries of waiting warps compete for issue slots with
-// the warps that do the work; roles whose waits are long and not latency-critical (producer,
-// epilogue) pass kSleepNs > 0 and sleep between polls.
-// Limit: a failed try_wait holds the warp for at least tens of cycles, so 2^24 retries are of the
-// order of a second.
-constexpr uint32_t kWaitRetryLimit = 1u << 24;
+// Bounded wait.  Returns false when the phase did not complete within `limit_cycles` SM clock
+// cycles (default: about half a second) or when another role of the CTA already gave up
+// (`*abort_flag` != 0); in the first case it records `code` in the flag.  The caller then leaves
+// its loop; nothing traps, the context stays usable and the host reads the code from the status
+// word.
+constexpr uint32_t kWaitLimit = 1u << 30;
 template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                          uint32_t retry_limit = kWaitRetryLimit) {
+                                          uint32_t limit_cycles = kWaitLimit) {
   if (mbar_try(bar, parity)) return true;
-  const uint32_t limit = kSleepNs > 0 ? (retry_limit >> 4) : retry_limit;
-  // eight polls per pass of the loop: the retry counter and the abort check cost integer-pipe
-  // instructions, which is what the dequantising warps next to a waiting warp are short of
+  const uint32_t t0 = static_cast<uint32_t>(clock());
+  // eight polls per pass of the loop: the clock and abort checks cost integer-pipe instructions,
+  // which is what the dequantising warps next to a waiting warp are short of
 #pragma unroll 1
-  for (uint32_t n = 0; n < limit; n += 8) {
+  for (;;) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if (kSleepNs > 0) __nanosleep(kSleepNs);
       if (mbar_try(bar, parity)) return true;
     }
     if (*abort_flag != 0) return false;
+    if (static_cast<uint32_t>(clock()) - t0 > limit_cycles) break;
   }
   atomicCAS(const_cast<int*>(abort_flag), 0, code);
   return false;

@@ -31,10 +31,18 @@ __global__ void __launch_bounds__(256) okc_repack(const RepackParams p) {
   const uint8_t* src = p.w + (static_cast<size_t>(ex) * p.rows + src_row) * (p.K / 2) + k0 / 2;
   const uint8_t* ssf = p.sf + (static_cast<size_t>(ex) * p.rows + src_row) * (p.K / 16) + k0 / 16;
   const uint4 raw = *reinterpret_cast<const uint4*>(src);
-  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t outw[4];
+  uint32_t stored[2];
 #pragma unroll
   for (int blk = 0; blk < 2; ++blk) {
+    // The scale goes into the image as scale_code(magnitude bits).  What that code cannot say is
+    // said through the codes, without changing any product: a zero scale clears the block's codes,
+    // a negative scale flips their signs.
+    const uint32_t sb = ssf[blk];
+    stored[blk] = scale_code(sb & 0x7Fu);
+    if ((sb & 0x7Fu) == 0u) { words[2 * blk] = 0u; words[2 * blk + 1] = 0u; }
+    if (sb & 0x80u) { words[2 * blk] ^= 0x88888888u; words[2 * blk + 1] ^= 0x88888888u; }
     const uint64_t codes = static_cast<uint64_t>(words[2 * blk]) | (static_cast<uint64_t>(words[2 * blk + 1]) << 32);
     uint64_t o = 0;
     for (int j = 0; j < 16; ++j)
@@ -47,7 +55,7 @@ __global__ void __launch_bounds__(256) okc_repack(const RepackParams p) {
                  (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes + static_cast<size_t>(tile) * kTileBytes;
   *reinterpret_cast<uint4*>(img + chunk * (kTileRows * 16) + row * 16) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
   *reinterpret_cast<uint16_t*>(img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2) =
-      static_cast<uint16_t>(ssf[0]) | (static_cast<uint16_t>(ssf[1]) << 8);
+      static_cast<uint16_t>(stored[0]) | (static_cast<uint16_t>(stored[1]) << 8);
 }
 
 

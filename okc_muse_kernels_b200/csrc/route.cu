@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(128) okc_gather_rows(const uint16_t* __restric
 }
 
 // Exercises the bounded wait on purpose: one warp waits on an mbarrier that nothing ever arrives
-// on, with a short retry limit; the wait gives up and the kernel reports it through the status
+// on, with a short limit; the wait gives up and the kernel reports it through the status
 // words exactly as the GEMM kernels do (no trap, the context stays usable).
 __global__ void okc_wait_timeout_probe(int32_t* status) {
   __shared__ uint64_t bar;
@@ -251,7 +251,7 @@ __global__ void okc_wait_timeout_probe(int32_t* status) {
     mbar_fence_init();
   }
   __syncthreads();
-  const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_code, 0x7e, 1u << 14);
+  const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_code, 0x7e, 1u << 20);
   __syncthreads();
   if (threadIdx.x == 0) {
     status[0] = ok ? OKC_OK : OKC_ERR_TIMEOUT;

@@ -19,6 +19,15 @@ streamed as K/256 *stages*; a stage is 36 864 contiguous bytes::
 Chunk c of row r holds K elements ``k0 + 32c .. k0 + 32c + 31`` (two 16-element scale blocks): four
 32-bit words ``(w0, w1)`` for block 0 and ``(w2, w3)`` for block 1, and the blocks' two scale bytes.
 
+Scale bytes
+-----------
+A block's E4M3 scale ``2**E * (1 + m/8)`` is kept as the byte ``16 + 8 * (E + 7) + m`` (``SCALE_CODE``;
+for a normal E4M3 byte b that is b + 16, the seven subnormals are normalised first).  Shifted left
+by four bits it is the exponent and top mantissa bits of a bf16, so one integer multiply-add,
+``byte * 0x00100010 + 0x76007600``, yields the bf16x2 ``{scale, scale} * 2**118``.  A scale of zero has
+no such code: the repack clears the block's codes instead (every product is zero either way); a
+negative scale is folded into the codes' sign bits.
+
 Bits inside a word pair
 -----------------------
 The 16 codes of a block are bit-permuted so that eight shift-and-mask operations produce eight
@@ -142,13 +151,36 @@ def _codes(packed: np.ndarray) -> np.ndarray:
     return np.stack((p & 0x0F, p >> 4), axis=-1).reshape(*p.shape[:-1], p.shape[-1] * 2)
 
 
+def _scale_code_table() -> np.ndarray:
+    """E4M3 magnitude bits (0..127) -> the byte kept in the stage image."""
+    t = np.zeros(128, dtype=np.uint8)
+    t[8:127] = np.arange(8, 127) + 16                 # normal: 2**(b//8 - 7) * (1 + (b%8)/8)
+    t[1:8] = (0, 8, 12, 16, 18, 20, 22)               # subnormal b * 2**-9, normalised
+    t[0] = 16                                         # zero: the codes are cleared, any finite scale will do
+    t[127] = 153                                      # NaN stays NaN
+    return t
+
+
+SCALE_CODE = _scale_code_table()
+
+
+def scale_code_value(code: np.ndarray) -> np.ndarray:
+    """What the device makes of a stored scale byte (undoing the 2**118): float32."""
+    pattern = (np.asarray(code, dtype=np.uint32) * np.uint32(16) + np.uint32(0x7600)) << np.uint32(16)
+    with np.errstate(invalid="ignore"):
+        return (pattern.view(np.float32).astype(np.float64) * 2.0 ** -118).astype(np.float32)
+
+
 def pack_tile_stage(packed_rows: np.ndarray, sf_rows: np.ndarray) -> np.ndarray:
     """One tile image: packed codes uint8 [128, 128] (K = 256) + scales uint8 [128, 16] -> uint8 [18432]."""
     codes = _codes(packed_rows).reshape(TILE_ROWS, CHUNKS, 2, 16)         # row, chunk, block, code
+    sc = np.asarray(sf_rows, dtype=np.uint8).reshape(TILE_ROWS, CHUNKS, 2)
+    mag = sc & 0x7F
+    codes = np.where((mag == 0)[..., None], 0, codes)                      # zero scale: clear the codes
+    codes = np.where((sc & 0x80 != 0)[..., None], codes ^ 8, codes)        # negative scale: flip the signs
     words = pack_block(codes)                                              # row, chunk, block, 2
     code_img = np.ascontiguousarray(words.transpose(1, 0, 2, 3)).view(np.uint8).reshape(-1)
-    sc = np.asarray(sf_rows, dtype=np.uint8).reshape(TILE_ROWS, CHUNKS, 2)
-    scale_img = np.ascontiguousarray(sc.transpose(1, 0, 2)).reshape(-1)
+    scale_img = np.ascontiguousarray(SCALE_CODE[mag].transpose(1, 0, 2)).reshape(-1)
     return np.concatenate((code_img, scale_img))
 
 

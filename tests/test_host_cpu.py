@@ -80,7 +80,7 @@ def test_cuda_bit_table_matches_layout_module():
 def test_tile_image_layout():
     rng = np.random.default_rng(2)
     packed = rng.integers(0, 256, (128, 128)).astype(np.uint8)
-    sf = rng.integers(0, 0x7F, (128, 16)).astype(np.uint8)
+    sf = rng.integers(1, 0x7F, (128, 16)).astype(np.uint8)
     img = layout.pack_tile_stage(packed, sf)
     assert img.shape == (layout.TILE_BYTES,)
     row, chunk = 37, 5
@@ -88,7 +88,7 @@ def test_tile_image_layout():
     vals = layout.regs_to_values(layout.unpack_block_regs(words.reshape(2, 2))).reshape(32)
     assert np.array_equal(vals, fp4.unpack_e2m1(packed[row, chunk * 16:(chunk + 1) * 16]))
     sc = img[layout.TILE_CODE_BYTES:].reshape(8, 128, 2)[chunk, row]
-    assert np.array_equal(sc, sf[row, 2 * chunk:2 * chunk + 2])
+    assert np.array_equal(sc, layout.SCALE_CODE[sf[row, 2 * chunk:2 * chunk + 2]])
 
 
 def test_torch_quantiser_matches_oracle_bit_exact():
@@ -153,3 +153,35 @@ def test_workload_table_matches_baseline_configs():
     assert (w["c4"].hidden, w["c4"].inter, w["c4"].n_experts, w["c4"].shared_inter) == (7168, 2048, 256, 2048)
     assert (w["c5"].tokens, w["c5"].n_experts, w["c5"].top_k, w["c5"].zipf_alpha) == (512, 160, 6, 1.2)
     assert synth.algorithmic_bytes(w["c2"], 1, 0) == 10616832      # 10.617 MB per touched expert
+
+
+def test_scale_code_is_exact_for_every_e4m3_byte():
+    """The stored scale byte, expanded the way the device does it (byte * 16 + 0x7600 as a bf16, over
+    2**118), is the E4M3 value for every finite non-zero byte; NaN stays NaN."""
+    from okc_muse_kernels_b200 import layout
+    from oracle import nvfp4_np as fp4
+    b = np.arange(1, 127, dtype=np.uint8)
+    want = fp4.e4m3_to_f32(b)
+    got = layout.scale_code_value(layout.SCALE_CODE[b])
+    assert np.array_equal(got, want)
+    assert np.isnan(layout.scale_code_value(layout.SCALE_CODE[127:128]))[0]
+    assert layout.SCALE_CODE.max() == 153 and int(layout.SCALE_CODE[1:127].max()) == 142
+
+
+def test_layout_pack_folds_zero_and_negative_scales_into_codes():
+    from okc_muse_kernels_b200 import layout
+    rng = np.random.default_rng(3)
+    packed = rng.integers(0, 256, (128, 128)).astype(np.uint8)
+    sf = rng.integers(1, 0x7F, (128, 16)).astype(np.uint8)
+    sf[0, 0] = 0          # zero scale
+    sf[1, 1] = 0x80 | 0x38  # -1.0
+    img = layout.pack_tile_stage(packed, sf)
+    words = img[:layout.TILE_CODE_BYTES].view(np.uint32).reshape(layout.CHUNKS, layout.TILE_ROWS, 2, 2)
+    vals = layout.regs_to_values(layout.unpack_block_regs(words))          # chunk, row, block, 16
+    from oracle import nvfp4_np as fp4
+    want = fp4.unpack_e2m1(packed).reshape(128, 8, 2, 16).transpose(1, 0, 2, 3).copy()
+    want[0, 0, 0] = 0.0
+    want[0, 1, 1] = -want[0, 1, 1]
+    assert np.array_equal(vals, want)
+    scales = img[layout.TILE_CODE_BYTES:].reshape(layout.CHUNKS, layout.TILE_ROWS, 2)
+    assert scales[0, 1, 1] == layout.SCALE_CODE[0x38]
