@@ -16,6 +16,7 @@ stream, max over ranks.  One JSON line is printed by rank 0.
 from __future__ import annotations
 
 import argparse
+import faulthandler
 import json
 import os
 import statistics
@@ -242,6 +243,8 @@ def run_gpu(args):
         torch.cuda.synchronize()
         dist.barrier()
         try:
+            if not args.ep_graphs:
+                raise RuntimeError("not requested")
             for ho, lo in own:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
@@ -250,7 +253,8 @@ def run_gpu(args):
             ep_timing = "CUDA-graph replay per step (kernels + NCCL collectives captured)"
         except Exception as exc:      # noqa: BLE001 - any capture failure means: run eagerly
             graphs = []
-            print(f"rank {rank}: graph capture of the expert-parallel step failed ({exc}); running eagerly", file=sys.stderr)
+            if args.ep_graphs:
+                print(f"rank {rank}: graph capture of the expert-parallel step failed ({exc}); running eagerly", file=sys.stderr)
         ok_flag = torch.tensor([1 if graphs else 0], device=dev)
         dist.all_reduce(ok_flag, op=dist.ReduceOp.MIN)
         if int(ok_flag.item()) == 0:
@@ -418,6 +422,16 @@ def run_gpu(args):
                 "step_ms_median": statistics.median(times_ms), "step_ms_min": min(times_ms)}
         print(json.dumps(line), flush=True)
     if world > 1:
+        captured = bool(graphs)
+        graphs.clear()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if captured:
+            # tearing down a communicator whose collectives were captured in CUDA graphs was seen to
+            # block; every rank is past its last collective here, so leave without the teardown
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
@@ -430,7 +444,11 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "c1", "c2", "c4", "c5"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--ep-graphs", type=int, default=1, choices=[0, 1],
+                    help="N > 1: capture the expert-parallel step (kernels + NCCL collectives) in CUDA graphs")
     args = ap.parse_args()
+    # a run that stops making progress prints every thread's stack and exits instead of hanging
+    faulthandler.dump_traceback_later(int(os.environ.get("OKC_BENCH_WATCHDOG_S", "900")), exit=True)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
