@@ -204,7 +204,16 @@ def run_gpu(args):
         plan = ep.shard_plan(wl.hidden, wl.inter, wl.n_experts, wl.top_k, world, rank, max_tokens=max(tokens, 16),
                              shared_inter=wl.shared_inter)
         weights = synth.make_weights(wl, device=dev, n_experts=plan.local_count, first_expert=plan.local_start)
-        layer = ep.ExpertParallelMoE(plan, tokens, weights=weights)
+        # the exchange steps over peer memory with this library's kernels; NCCL collectives if the
+        # ranks' buffers cannot be mapped into each other (every rank takes the same branch)
+        layer = None
+        if args.exchange == "peer":
+            try:
+                layer = ep.ExpertParallelMoE(plan, tokens, weights=weights, exchange="peer")
+            except Exception as exc:      # noqa: BLE001
+                print(f"rank {rank}: peer-memory exchange unavailable ({exc}); using NCCL collectives", file=sys.stderr)
+        if layer is None:
+            layer = ep.ExpertParallelMoE(plan, tokens, weights=weights, exchange="nccl")
         state = layer.state
     del weights
     torch.cuda.empty_cache()
@@ -232,7 +241,8 @@ def run_gpu(args):
                 okc.moe_step(h, lg, state, out=o)
             graphs.append(g)
 
-    ep_timing = "eager launches + NCCL collectives per step"
+    exch = "" if world == 1 else ("peer-memory exchange kernels" if layer.exchange == "peer" else "NCCL collectives")
+    ep_timing = f"eager launches + {exch} per step"
     if world > 1:
         # the expert-parallel step (two all-gathers, five kernels, a reduce-scatter, a cast) as one CUDA
         # graph per routing seed: at 8 ranks a rank's kernels take about as long as the host needs to
@@ -250,7 +260,7 @@ def run_gpu(args):
                 with torch.cuda.graph(g):
                     layer.step(ho, lo)
                 graphs.append(g)
-            ep_timing = "CUDA-graph replay per step (kernels + NCCL collectives captured)"
+            ep_timing = f"CUDA-graph replay per step (kernels + {exch} captured)"
         except Exception as exc:      # noqa: BLE001 - any capture failure means: run eagerly
             graphs = []
             if args.ep_graphs:
@@ -259,7 +269,7 @@ def run_gpu(args):
         dist.all_reduce(ok_flag, op=dist.ReduceOp.MIN)
         if int(ok_flag.item()) == 0:
             graphs = []
-            ep_timing = "eager launches + NCCL collectives per step"
+            ep_timing = f"eager launches + {exch} per step"
 
     def step(i):
         j = i % len(SEEDS)
@@ -303,6 +313,10 @@ def run_gpu(args):
     rc, detail = okc.read_status(state)
     if rc != 0:
         raise SystemExit(f"device status {rc} detail {detail:#x}")
+    if world > 1 and layer.peer is not None:
+        rc, detail = layer.peer.read_status()
+        if rc != 0:
+            raise SystemExit(f"rank {rank}: exchange status {rc} detail {detail:#x}")
 
     if world > 1:
         t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
@@ -418,7 +432,7 @@ def run_gpu(args):
                            "timing": "CUDA-graph replay per step" if world == 1 else ep_timing,
                            "touched_experts_per_seed": touched, "routing_seeds": list(SEEDS)},
                 "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-                "gpu_launches": _lib.lib().okc_moe_launches_per_step() * args.steps + (args.steps if world > 1 else 0),
+                "gpu_launches": (_lib.lib().okc_moe_launches_per_step() + (0 if world == 1 else 2 if layer.exchange == "peer" else 1)) * args.steps,
                 "step_ms_median": statistics.median(times_ms), "step_ms_min": min(times_ms)}
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -444,6 +458,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "c1", "c2", "c4", "c5"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: the all-gather / reduce-scatter through this library's peer-memory kernels or NCCL")
     ap.add_argument("--ep-graphs", type=int, default=1, choices=[0, 1],
                     help="N > 1: capture the expert-parallel step (kernels + NCCL collectives) in CUDA graphs")
     args = ap.parse_args()

@@ -162,6 +162,42 @@ int okc_moe_step_static_scratch(const okc_moe_plan* plan, const void* packed_w13
                                 const void* post_norm_w, int32_t* ids, float* weights, void* out,
                                 int out_f32, okc_stream_t stream);
 
+/*
+ * The exchange steps of the expert-parallel layer over peer memory (NVLink / NVSwitch), for one
+ * process per GPU.  No counterpart in the reference: its shards never exchange anything (the expert
+ * all-reduce is not run, muse_moe_w4a16/baseline.py:8).
+ *
+ * Every rank owns one exchange buffer of okc_ep_buffer_bytes() bytes, zeroed once before the first
+ * step, and maps the buffers of all ranks into its address space (CUDA IPC or any other peer
+ * mapping; the caller's business).  Rank r owns token rows [r*T/world, (r+1)*T/world) of the step.
+ *  - okc_ep_gather_tokens: stores this rank's rows (hidden bf16 [T/world, hidden_stride], logits f32
+ *    [T/world, E]) into every rank's buffer and returns when every rank's rows have arrived here:
+ *    afterwards okc_ep_views' hidden_all [T, H] / logits_all [T, E] hold the whole step's tokens.
+ *  - the caller then runs okc_moe_step on them with out = okc_ep_views' partial (f32 [T, H], out_f32 = 1).
+ *  - okc_ep_reduce_scatter: out_bf16 [T/world, H] = sum over ranks (rank order) of their partial
+ *    rows of this rank's tokens, rounded once.
+ * All ranks must make the same calls in the same order.  The waits on other ranks are bounded (five
+ * seconds); one that runs out is reported by okc_ep_read_status (OKC_ERR_TIMEOUT, detail 0x100 + rank
+ * for the gather, 0x200 + rank for the reduce) and the step's result is then undefined.
+ */
+#define OKC_EP_MAX_RANKS 16
+typedef struct okc_ep_comm {
+  int32_t rank, world;
+  int32_t tokens;      /* T of the whole step, a multiple of world */
+  int32_t hidden;      /* H, a multiple of 256 */
+  int32_t n_experts;   /* E, a multiple of 4 */
+  int32_t reserved[3]; /* must be zero */
+  void* peer[OKC_EP_MAX_RANKS]; /* this process's address of rank r's buffer; peer[rank] is its own */
+} okc_ep_comm;
+
+uint64_t okc_ep_buffer_bytes(int32_t tokens, int32_t hidden, int32_t n_experts);
+int okc_ep_views(const okc_ep_comm* comm, void** hidden_all, void** logits_all, void** partial);
+int okc_ep_gather_tokens(const okc_ep_comm* comm, const void* hidden_own, int64_t hidden_stride,
+                         const float* logits_own, okc_stream_t stream);
+int okc_ep_reduce_scatter(const okc_ep_comm* comm, void* out_bf16, okc_stream_t stream);
+/* Synchronises `stream`; returns the status kept in this rank's buffer and clears it. */
+int okc_ep_read_status(const okc_ep_comm* comm, okc_stream_t stream, int32_t* detail);
+
 /* Copies the sorted-route tables out of `workspace` for inspection (host or device pointers are
  * NOT interchangeable: all four are device pointers; any may be NULL).  counts: int32
  * [expert_slots]; sorted: int32 [T*routes_per_token] (route index t*routes_per_token+slot per

@@ -34,8 +34,18 @@ class Sizes(C.Structure):
                 ("expert_slots", C.c_uint32), ("routes_per_token", C.c_uint32)]
 
 
+EP_MAX_RANKS = 16
+
+
+class EpComm(C.Structure):
+    """okc_ep_comm"""
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("tokens", C.c_int32), ("hidden", C.c_int32),
+                ("n_experts", C.c_int32), ("reserved", C.c_int32 * 3), ("peer", C.c_void_p * EP_MAX_RANKS)]
+
+
 _P = C.c_void_p
 _PLAN = C.POINTER(Plan)
+_COMM = C.POINTER(EpComm)
 # name -> (restype, argtypes); every symbol include/okc_moe.h declares
 SIGNATURES = {
     "okc_moe_version": (C.c_int, []),
@@ -57,6 +67,11 @@ SIGNATURES = {
     "okc_moe_unpack_bf16": (C.c_int, [_PLAN, _P, C.c_int, C.c_int, _P, _P]),
     "okc_moe_probe_wait_timeout": (C.c_int, [_P, _P]),
     "okc_moe_read_status": (C.c_int, [_P, _P, C.POINTER(C.c_int32)]),
+    "okc_ep_buffer_bytes": (C.c_uint64, [C.c_int32, C.c_int32, C.c_int32]),
+    "okc_ep_views": (C.c_int, [_COMM, C.POINTER(_P), C.POINTER(_P), C.POINTER(_P)]),
+    "okc_ep_gather_tokens": (C.c_int, [_COMM, _P, C.c_int64, _P, _P]),
+    "okc_ep_reduce_scatter": (C.c_int, [_COMM, _P, _P]),
+    "okc_ep_read_status": (C.c_int, [_COMM, _P, C.POINTER(C.c_int32)]),
 }
 
 _lib = None

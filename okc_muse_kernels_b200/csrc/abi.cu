@@ -356,6 +356,71 @@ int okc_moe_read_status(const void* workspace, okc_stream_t stream_, int32_t* de
 }
 
 // ---------------------------------------------------------------------------------------------
+// Expert-parallel exchange over peer memory.
+static bool ep_params(const okc_ep_comm* c, EpParams& p) {
+  if (!c || c->world < 1 || c->world > kEpMaxRanks || c->rank < 0 || c->rank >= c->world) return false;
+  if (c->tokens <= 0 || (c->tokens % c->world) != 0 || c->hidden <= 0 || (c->hidden % 256) != 0) return false;
+  if (c->n_experts <= 0 || (c->n_experts % 4) != 0) return false;
+  for (int i = 0; i < 3; ++i)
+    if (c->reserved[i] != 0) return false;
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < c->world; ++r) {
+    if (!c->peer[r] || !aligned(c->peer[r], 256)) return false;
+    p.peer[r] = static_cast<uint8_t*>(c->peer[r]);
+  }
+  const EpLayout l = ep_layout(c->tokens, c->hidden, c->n_experts);
+  p.rank = c->rank; p.world = c->world; p.tokens = c->tokens; p.H = c->hidden; p.E = c->n_experts;
+  p.off_hidden = l.off_hidden; p.off_logits = l.off_logits; p.off_partial = l.off_partial;
+  return true;
+}
+
+uint64_t okc_ep_buffer_bytes(int32_t tokens, int32_t hidden, int32_t n_experts) {
+  if (tokens <= 0 || hidden <= 0 || n_experts <= 0) return 0;
+  return ep_layout(tokens, hidden, n_experts).total;
+}
+
+int okc_ep_views(const okc_ep_comm* comm, void** hidden_all, void** logits_all, void** partial) {
+  EpParams p;
+  if (!ep_params(comm, p)) return OKC_ERR_BAD_ARG;
+  uint8_t* mine = p.peer[p.rank];
+  if (hidden_all) *hidden_all = mine + p.off_hidden;
+  if (logits_all) *logits_all = mine + p.off_logits;
+  if (partial) *partial = mine + p.off_partial;
+  return OKC_OK;
+}
+
+int okc_ep_gather_tokens(const okc_ep_comm* comm, const void* hidden_own, int64_t hidden_stride,
+                         const float* logits_own, okc_stream_t stream) {
+  EpParams p;
+  if (!ep_params(comm, p)) return OKC_ERR_BAD_ARG;
+  if (!hidden_own || !logits_own || !aligned(hidden_own, 16) || !aligned(logits_own, 16)) return OKC_ERR_BAD_ARG;
+  if (hidden_stride < p.H || (hidden_stride % 8) != 0) return OKC_ERR_BAD_ARG;
+  p.hidden_own = static_cast<const uint16_t*>(hidden_own); p.hidden_stride = hidden_stride; p.logits_own = logits_own;
+  return launch_ep_push(p, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+int okc_ep_reduce_scatter(const okc_ep_comm* comm, void* out_bf16, okc_stream_t stream) {
+  EpParams p;
+  if (!ep_params(comm, p)) return OKC_ERR_BAD_ARG;
+  if (!out_bf16 || !aligned(out_bf16, 8)) return OKC_ERR_BAD_ARG;
+  p.out = static_cast<uint16_t*>(out_bf16);
+  return launch_ep_reduce(p, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+int okc_ep_read_status(const okc_ep_comm* comm, okc_stream_t stream_, int32_t* detail) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  EpParams p;
+  if (!ep_params(comm, p)) return OKC_ERR_BAD_ARG;
+  int32_t host[2] = {0, 0};
+  int32_t* st = reinterpret_cast<int32_t*>(p.peer[p.rank]) + kEpCtrlStatus;
+  if (cudaMemcpyAsync(host, st, sizeof(host), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (cudaMemsetAsync(st, 0, sizeof(host), stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (detail) *detail = host[1];
+  return host[0];
+}
+
+// ---------------------------------------------------------------------------------------------
 // A step that needs no workspace from the caller.
 //
 // Some hosts of this library may not allocate device memory at all once they are running: an

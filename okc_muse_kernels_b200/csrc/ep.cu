@@ -1,0 +1,180 @@
+// The two exchange steps of the expert-parallel MoE step, written against peer memory: every rank
+// maps every other rank's exchange buffer (NVLink / NVSwitch peer access) and the kernels below
+// move the data with ordinary stores and loads and order it with system-scope flags.
+//
+//   push_tokens:  rank r stores its token block (hidden rows, router logits) into every rank's
+//                 buffer, then raises flag_in[r] on every rank and waits until all ranks raised
+//                 theirs here: an all-gather in one kernel.
+//   pull_reduce:  rank r raises flag_rs[r] on every rank ("my partial sums are complete"), waits
+//                 for the flags of the others, reads its own token rows of every rank's FP32 partial
+//                 sums (rank order, so the sum is deterministic) and writes them as bf16: a
+//                 reduce-scatter and the cast in one kernel.
+//
+// The reference has no counterpart: its expert all-reduce is not run (muse_moe_w4a16/baseline.py:8).
+//
+// No buffer is double-buffered and no "done reading" flag exists, because the order of a step
+// already protects the data: a rank pushes the tokens of step n+1 only after its pull_reduce of step
+// n, which waited for every rank's "partial sums complete" flag of step n, which a rank raises after
+// its last read of the step-n tokens; and a rank overwrites its partial sums in step n+1 only after
+// its push_tokens of step n+1 saw every rank's step-n+1 flag, which a rank raises after its
+// pull_reduce of step n, i.e. after its last read of anybody's step-n partial sums.
+//
+// Every wait is bounded (kEpWaitNs of wall time); a wait that runs out records a code in the
+// buffer's status words and the kernel carries on to its end: nothing traps.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/okc_moe.h"
+#include "params.cuh"
+
+namespace okc {
+
+namespace {
+
+constexpr unsigned long long kEpWaitNs = 5000000000ull;   // 5 s: peers may start a step late
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Waits until *flag >= want.  Returns false after kEpWaitNs.
+__device__ __forceinline__ bool wait_flag(const int32_t* flag, int32_t want) {
+  if (ld_acquire_sys(flag) >= want) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 16; ++i) {
+      if (ld_acquire_sys(flag) >= want) return true;
+      __nanosleep(200);
+    }
+    if (global_ns() - t0 > kEpWaitNs) return false;
+  }
+}
+
+__device__ __forceinline__ int32_t* ctrl_of(uint8_t* buf) { return reinterpret_cast<int32_t*>(buf); }
+__device__ __forceinline__ int32_t* flags_in_of(uint8_t* buf) { return reinterpret_cast<int32_t*>(buf + kEpOffFlagsIn); }
+__device__ __forceinline__ int32_t* flags_rs_of(uint8_t* buf) { return reinterpret_cast<int32_t*>(buf + kEpOffFlagsRs); }
+
+}  // namespace
+
+// grid (row groups, world): CTA (x, r) stores rows x, x + gridDim.x, ... of this rank's block into
+// rank r's buffer.  The last CTA to finish signals and waits.
+__global__ void __launch_bounds__(256) okc_ep_push_tokens(const EpParams p) {
+  uint8_t* mine = p.peer[p.rank];
+  uint8_t* dest = p.peer[blockIdx.y];
+  const int tb = p.tokens / p.world;
+  const int hv = p.H / 8;        // 16-byte vectors per hidden row
+  const int lv = p.E / 4;        // 16-byte vectors per logits row
+  for (int row = blockIdx.x; row < tb; row += gridDim.x) {
+    const uint4* hs = reinterpret_cast<const uint4*>(p.hidden_own + static_cast<size_t>(row) * p.hidden_stride);
+    uint4* hd = reinterpret_cast<uint4*>(dest + p.off_hidden) + (static_cast<size_t>(p.rank) * tb + row) * hv;
+    for (int i = threadIdx.x; i < hv; i += blockDim.x) hd[i] = hs[i];
+    const uint4* ls = reinterpret_cast<const uint4*>(p.logits_own + static_cast<size_t>(row) * p.E);
+    uint4* ld = reinterpret_cast<uint4*>(dest + p.off_logits) + (static_cast<size_t>(p.rank) * tb + row) * lv;
+    for (int i = threadIdx.x; i < lv; i += blockDim.x) ld[i] = ls[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  int32_t* ctrl = ctrl_of(mine);
+  if (threadIdx.x == 0) {
+    const int total = gridDim.x * gridDim.y;
+    s_last = (atomicAdd(&ctrl[kEpCtrlDoneIn], 1) == total - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // every CTA of this rank has stored (and fenced) its rows: tell everybody, then wait for everybody
+  __threadfence_system();
+  const int32_t seq = ctrl[kEpCtrlSeqIn] + 1;
+  if (threadIdx.x < p.world) {
+    st_release_sys(flags_in_of(p.peer[threadIdx.x]) + p.rank, seq);
+    if (!wait_flag(flags_in_of(mine) + threadIdx.x, seq)) {
+      atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
+      atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x100 | threadIdx.x);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ctrl[kEpCtrlDoneIn] = 0;
+    ctrl[kEpCtrlSeqIn] = seq;
+  }
+}
+
+// grid (H / 1024, token rows of this rank): thread = four columns of one row.
+__global__ void __launch_bounds__(256) okc_ep_pull_reduce(const EpParams p) {
+  uint8_t* mine = p.peer[p.rank];
+  int32_t* ctrl = ctrl_of(mine);
+  const int tb = p.tokens / p.world;
+  const int32_t seq = ctrl[kEpCtrlSeqRs] + 1;   // changed only by the last CTA, after every CTA read it
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < p.world) {
+    // this rank's partial sums were written by the kernels before this one in the stream
+    __threadfence_system();
+    st_release_sys(flags_rs_of(p.peer[threadIdx.x]) + p.rank, seq);
+  }
+  if (threadIdx.x < p.world) {
+    if (!wait_flag(flags_rs_of(mine) + threadIdx.x, seq)) {
+      atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
+      atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x200 | threadIdx.x);
+    }
+  }
+  __syncthreads();
+  const int row = blockIdx.y;
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (col < p.H) {
+    const size_t off = (static_cast<size_t>(p.rank) * tb + row) * p.H + col;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < p.world; ++r) {       // rank order: the same sum on every run
+      const float4 v = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r] + p.off_partial) + off);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p.out + static_cast<size_t>(row) * p.H + col) = o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int total = gridDim.x * gridDim.y;
+    if (atomicAdd(&ctrl[kEpCtrlDoneRs], 1) == total - 1) {
+      ctrl[kEpCtrlDoneRs] = 0;
+      ctrl[kEpCtrlSeqRs] = seq;
+    }
+  }
+}
+
+cudaError_t launch_ep_push(const EpParams& p, cudaStream_t stream) {
+  const int tb = p.tokens / p.world;
+  int gx = 128 / p.world;
+  if (gx < 1) gx = 1;
+  if (gx > tb) gx = tb;
+  okc_ep_push_tokens<<<dim3(gx, p.world), 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_reduce(const EpParams& p, cudaStream_t stream) {
+  const int tb = p.tokens / p.world;
+  okc_ep_pull_reduce<<<dim3((p.H + 1023) / 1024, tb), 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace okc

@@ -83,6 +83,25 @@ inline bool make_geometry(const okc_moe_plan& p, Geometry& g) {
   return true;
 }
 
+// Exchange buffer of the expert-parallel step (one per rank, the same layout on every rank, mapped
+// by every rank): control words used by the owner alone, two flag arrays written by the peers, then
+// the gathered token rows, the gathered router logits and this rank's FP32 partial sums.
+constexpr int kEpMaxRanks = OKC_EP_MAX_RANKS;
+constexpr size_t kEpOffFlagsIn = 256, kEpOffFlagsRs = 512, kEpOffData = 1024;
+enum EpCtrlWord { kEpCtrlSeqIn = 0, kEpCtrlSeqRs = 1, kEpCtrlDoneIn = 2, kEpCtrlDoneRs = 3, kEpCtrlStatus = 4, kEpCtrlDetail = 5 };
+struct EpLayout {
+  size_t off_hidden, off_logits, off_partial, total;
+};
+inline EpLayout ep_layout(int tokens, int H, int E) {
+  EpLayout l;
+  size_t o = kEpOffData;
+  l.off_hidden = o;   o = align_up(o + static_cast<size_t>(tokens) * H * 2, 1024);
+  l.off_logits = o;   o = align_up(o + static_cast<size_t>(tokens) * E * 4, 1024);
+  l.off_partial = o;  o = align_up(o + static_cast<size_t>(tokens) * H * 4, 1024);
+  l.total = o;
+  return l;
+}
+
 #ifdef __CUDACC__
 // One stored scale byte -> bf16x2 {scale, scale} * 2^118, with one integer multiply-add (issued to
 // the FMA pipe, which has room; the mask / rotate work saturates the integer pipe).

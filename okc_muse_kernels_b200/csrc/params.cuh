@@ -73,6 +73,19 @@ struct MoeGemmParams {
 cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream);
 int gemm_stages_for(int ncap);
 
+// The exchange kernels of the expert-parallel step (ep.cu).
+struct EpParams {
+  uint8_t* peer[kEpMaxRanks];   // this process's mapping of every rank's exchange buffer
+  int rank, world, tokens, H, E;
+  size_t off_hidden, off_logits, off_partial;
+  const uint16_t* hidden_own;   // push: bf16 [tokens / world, hidden_stride]
+  int64_t hidden_stride;
+  const float* logits_own;      // push: f32 [tokens / world, E]
+  uint16_t* out;                // reduce: bf16 [tokens / world, H]
+};
+cudaError_t launch_ep_push(const EpParams& p, cudaStream_t stream);
+cudaError_t launch_ep_reduce(const EpParams& p, cudaStream_t stream);
+
 struct CombineParams {
   const float* y;
   const int32_t* pos;

@@ -289,6 +289,24 @@ def test_batch_sweep_rows_match_config2_single_rows(T):
     _check_out(out[sub], ref, f"batch {T}")
 
 
+def test_experts_run_again_on_the_same_routes():
+    """The GEMM launch leaves its counters at zero, so the expert phase can be repeated without a new
+    route call (three times here), with bit-identical results."""
+    dev = _dev()
+    wl = synth.Workload("r", 24, 512, 256, 16, 4)
+    w = synth.make_weights(wl, seed=5, device=dev)
+    state = okc.prepare(w, okc.MoEPlan(hidden=512, inter=256, n_experts=16, top_k=4, max_tokens=32))
+    hidden, logits = synth.make_inputs(wl, seed=6, device=dev)
+    want = okc.moe_step(hidden, logits, state).clone()
+    _status_ok(state)
+    okc.route(logits, state)
+    for _ in range(3):
+        out = torch.empty_like(want)
+        okc.experts_profiled(hidden, state, out)
+        _status_ok(state)
+        assert torch.equal(out, want)
+
+
 def test_zipf_routing_hot_expert_chunks():
     """Config 5's routing skew at a narrower width: one expert takes > 128 tokens, so its rows are cut
     into several work items."""

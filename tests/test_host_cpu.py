@@ -18,8 +18,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "okc_moe.h")).read()
-    declared = set(re.findall(r"\b(okc_moe_[a-z0-9_]+)\s*\(", header))
-    declared -= {"okc_moe_plan", "okc_moe_sizes", "okc_moe_error"}
+    declared = set(re.findall(r"\b(okc_(?:moe|ep)_[a-z0-9_]+)\s*\(", header))
+    declared -= {"okc_moe_plan", "okc_moe_sizes", "okc_moe_error", "okc_ep_comm", "okc_ep_buffer_bytes"} - set(_lib.SIGNATURES)
     assert declared, "no declarations found"
     handle = C.CDLL(_lib.LIB_PATH)
     for name in sorted(declared):
@@ -56,6 +56,13 @@ def test_null_and_range_arguments_are_rejected_before_any_launch():
         == _lib.OKC_ERR_BAD_ARG
     assert lib.okc_moe_repack(C.byref(cp), None, None, None, None, 0, 1, None, None, None) == _lib.OKC_ERR_BAD_ARG
     assert lib.okc_moe_read_status(None, None, None) == _lib.OKC_ERR_BAD_ARG
+    # expert-parallel exchange: sizes, and argument checks that touch no GPU
+    assert lib.okc_ep_buffer_bytes(128, 7168, 256) >= 128 * 7168 * 6 + 128 * 256 * 4
+    comm = _lib.EpComm(rank=2, world=2, tokens=128, hidden=7168, n_experts=256)
+    assert lib.okc_ep_gather_tokens(C.byref(comm), None, 7168, None, None) == _lib.OKC_ERR_BAD_ARG   # rank >= world
+    comm = _lib.EpComm(rank=0, world=2, tokens=127, hidden=7168, n_experts=256)
+    assert lib.okc_ep_reduce_scatter(C.byref(comm), None, None) == _lib.OKC_ERR_BAD_ARG            # T % world
+    assert lib.okc_ep_views(None, None, None, None) == _lib.OKC_ERR_BAD_ARG
 
 
 def test_bit_permutation_round_trip():
