@@ -99,6 +99,70 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+class NvmlSampler:
+    """Reads SM clock and clock-event reasons of one GPU through NVML from a thread of this process
+    every few milliseconds (read-only queries).  Same interface as ClockSampler, which it falls back
+    to when NVML cannot be loaded: nvidia-smi needs a good part of a second before its first sample,
+    more than a short timed region lasts."""
+    REASONS = ((0x4, "sw_power_cap"), (0x8, "hw_slowdown"), (0x20, "sw_thermal_slowdown"), (0x40, "hw_thermal_slowdown"))
+
+    def __init__(self, index: int):
+        self.index = index
+        self.fallback = None
+        self.samples: list[tuple[int, int]] = []
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            try:
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:      # noqa: BLE001 - older torch / NVML: fall back to the ordinal
+                handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nvml, self.handle = pynvml, handle
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        except Exception:          # noqa: BLE001
+            self.nvml = None
+            self.fallback = ClockSampler(index)
+
+    def start(self):
+        if self.fallback is not None:
+            return self.fallback.start()
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+
+    def _run(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                mhz = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                try:
+                    mask = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except AttributeError:
+                    mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((int(mhz), int(mask)))
+            except Exception:      # noqa: BLE001
+                pass
+            time.sleep(0.003)
+
+    def mark(self):
+        """Samples taken before this call are dropped (call when the timed region starts)."""
+        self.samples.clear()
+
+    def stop(self) -> dict:
+        if self.fallback is not None:
+            return self.fallback.stop()
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        sm = [m for m, _ in self.samples]
+        reasons = sorted({name for _, mask in self.samples for bit, name in self.REASONS if mask & bit})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(sm), "reasons": reasons}
+
+
 def _touched(ids: np.ndarray, lo: int, cnt: int) -> int:
     u = np.unique(ids)
     return int(((u >= lo) & (u < lo + cnt)).sum())
@@ -287,9 +351,10 @@ def run_gpu(args):
     bytes_per_seed = [synth.algorithmic_bytes(wl, n, tokens if world == 1 else tokens, shared=bool(wl.shared_inter))
                       for n in touched]
 
-    # the clock sampler starts before the warm-up so that nvidia-smi is already reporting when the
-    # (short) timed region runs; every sample it returns was taken under this workload
-    sampler = ClockSampler(local_rank)
+    # the clock sampler starts before the warm-up; samples from before the timed region are dropped
+    # when NVML is read in-process (the nvidia-smi fallback keeps them: it is slow to start, and they
+    # too were taken under this workload)
+    sampler = NvmlSampler(local_rank)
     if rank == 0:
         sampler.start()
     for i in range(args.warmup):
@@ -298,6 +363,8 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    if rank == 0 and sampler.fallback is None:
+        sampler.mark()
     for i in range(args.steps):
         flush_l2()
         ev[i][0].record()
