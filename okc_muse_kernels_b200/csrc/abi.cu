@@ -50,7 +50,7 @@ static std::atomic<int> g_dbg_flags{0};
 #define OKC_DBG_SPLIT 0
 #endif
 
-static int ncap_for(int T) { return chunk_rows_for(T); }
+static int ncap_for(const okc_moe_plan* plan, int T) { return chunk_rows_for(T, plan->top_k, plan->n_experts); }
 
 static int sm_count() {
   int dev = 0, n = 0;
@@ -110,7 +110,7 @@ static int route_common(const okc_moe_plan* plan, const float* logits, const int
   p.meta = w.meta; p.counts = w.counts; p.items = w.items; p.sorted = w.sorted; p.pos = w.pos; p.wsorted = w.wsorted;
   p.T = T; p.E = plan->n_experts; p.k = plan->top_k; p.kk = g.kk; p.slots = g.slots;
   p.local_start = plan->local_start; p.local_count = plan->local_count; p.has_shared = plan->shared_inter ? 1 : 0;
-  p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items; p.chunk_rows = chunk_rows_for(T);
+  p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items; p.chunk_rows = chunk_rows_for(T, plan->top_k, plan->n_experts);
   return launch_route(p, stream) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
 }
 
@@ -225,7 +225,7 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   if (sms <= 0) return OKC_ERR_CUDA;
   Ws w = carve(workspace, g);
   const int R = T * g.kk;
-  const int ncap = ncap_for(T);
+  const int ncap = ncap_for(plan, T);
 
   if (ev && cudaEventRecord(ev[0], stream) != cudaSuccess) return OKC_ERR_CUDA;
   if (launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, w.done, g.max_items, stream) != cudaSuccess)

@@ -18,9 +18,13 @@ constexpr int kTileScaleBytes = kChunks * kTileRows * 2;   // 2048
 constexpr int kTileBytes = kTileCodeBytes + kTileScaleBytes;
 constexpr int kStageBytes = 2 * kTileBytes;    // 36864: two tiles (gate+up, or two row tiles of w2)
 constexpr int kChunkRows = 32;                 // most rows (tokens) of one work item
-// Rows per work item for a step of T tokens: 16 for decode-sized steps (the accumulators of eight
-// issuers then fit TMEM twice, so the epilogue overlaps the next unit), 32 beyond.
-__host__ __device__ inline int chunk_rows_for(int T) { return T <= 64 ? 16 : kChunkRows; }
+// Rows per work item for a step of T tokens, k routes each, over E experts: 16 while the step is
+// decode-sized or an expert gets 8 rows or fewer on average (the accumulators of eight issuers then
+// fit TMEM twice, so the epilogue overlaps the next unit, and the stage ring is a stage deeper);
+// 32 beyond, where 16-row items would stream and dequantise most experts' weights twice.
+__host__ __device__ inline int chunk_rows_for(int T, int k, int E) {
+  return (T <= 64 || static_cast<long long>(T) * k <= 8LL * E) ? 16 : kChunkRows;
+}
 constexpr int kMaxSlots = 513;                 // 512 experts + shared
 constexpr int kMaxRoutes = 16384;              // routes (tokens x routes per token) one step may hold
 

@@ -121,7 +121,7 @@ def test_route_ids_bit_exact(T, E, k):
     assert np.allclose(wts.cpu().numpy(), ref_w, rtol=2e-6, atol=1e-9)
     # the sort tables, bit-exact against the oracle's stable sort
     s = okc.sorted_routes(state, T)
-    ref = moe_np.sort_routes(ref_ids, 0, E, chunk=16 if T <= 64 else 32)   # rows per work item
+    ref = moe_np.sort_routes(ref_ids, 0, E, chunk=16 if (T <= 64 or T * k <= 8 * E) else 32)   # rows per work item
     assert np.array_equal(s["counts"].cpu().numpy(), ref["counts"])
     n = len(ref["sorted"])
     assert np.array_equal(s["sorted"].cpu().numpy()[:n], ref["sorted"])
