@@ -141,7 +141,7 @@ const char* okc_moe_strerror(int code) {
   }
 }
 
-int okc_moe_launches_per_step(void) { return 4; }
+int okc_moe_launches_per_step(void) { return 5; }
 
 int okc_moe_query(const okc_moe_plan* plan, okc_moe_sizes* out) {
   Geometry g;

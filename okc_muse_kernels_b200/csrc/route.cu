@@ -1,4 +1,4 @@
-// Router (softmax top-k) and token -> expert sort, one CTA per step.
+// Router (softmax top-k: a warp per token over many CTAs) and token -> expert sort (one CTA per step).
 //
 // Behaviour follows the reference's routing + sort kernels (different algorithm, same results):
 //   * top-k with ties to the lowest index       muse_decode_layer/layer.py:394-406 (_routing)
@@ -14,7 +14,81 @@ namespace okc {
 constexpr int kRouteThreads = 1024;
 constexpr int kRouteWarps = kRouteThreads / 32;
 
+// Optional phase clock of the route kernel (-DOKC_WAIT_PROFILE): thread 0's clock at each phase end.
+#ifdef OKC_WAIT_PROFILE
+__device__ long long g_route_prof[8];
+#define OKC_ROUTE_MARK(i) { if (threadIdx.x == 0) g_route_prof[i] = clock64(); }
+extern "C" int okc_moe_debug_route_profile(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_route_prof, sizeof(g_route_prof)) == cudaSuccess ? 0 : -3;
+}
+#else
+#define OKC_ROUTE_MARK(i)
+#endif
+
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+// Softmax top-k of the router logits, one warp per token, eight tokens per CTA (the tokens of a
+// step spread over many SMs: one CTA doing all of them is bound by its own instruction issue).
+// PER = candidates per lane (expert e sits in lane e % 32, slot e / 32).  Every lane keeps the best
+// of its untaken candidates; a round is a warp arg-max over those 32 values, after which only the
+// winner's lane looks for its next best.  Order: larger logit first, ties to the lower expert id,
+// NaN never wins.
+template <int PER>
+__global__ void __launch_bounds__(256) okc_route_topk(const float* __restrict__ logits, int T, int E, int k,
+                                                      int32_t* __restrict__ ids_out, float* __restrict__ wts_out) {
+  griddep_launch_dependents();   // the sort kernel may set itself up; it waits for this grid to complete
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  float v[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int e = lane + 32 * j;
+    const float x = (e < E) ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    v[j] = (x == x) ? x : -INFINITY;
+  }
+  uint32_t taken = 0;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int e = lane + 32 * j;
+    if (e < E && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; }
+  }
+  float my_val = 0.f;
+  int my_id = 0;
+  for (int r = 0; r < k; ++r) {
+    float wv = bv;
+    int wi = bi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+      if (better(ov, oi, wv, wi)) { wv = ov; wi = oi; }
+    }
+    if (lane == r) { my_val = wv; my_id = wi; }
+    if (wi == bi) {
+      // this lane held the winner: next best of what it has left
+      taken |= 1u << (wi >> 5);
+      bv = -INFINITY;
+      bi = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int e = lane + 32 * j;
+        if (e < E && !((taken >> j) & 1u) && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; }
+      }
+    }
+  }
+  const float top = __shfl_sync(0xffffffffu, my_val, 0);
+  const float ex = (lane < k) ? expf(my_val - top) : 0.f;
+  float sum = ex;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane < k) {
+    ids_out[t * k + lane] = my_id;
+    wts_out[t * k + lane] = ex / sum;
+  }
+}
 
 __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RouteParams p) {
   extern __shared__ int32_t sm[];
@@ -31,65 +105,23 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) s_nact = 0;
+  griddep_wait();   // the ids may come from the top-k kernel launched just before
+  OKC_ROUTE_MARK(0)
 
   for (int i = tid; i < kRouteWarps * p.slots; i += kRouteThreads) whist[i] = 0;
   for (int i = tid; i < R; i += kRouteThreads) p.sorted[i] = -1;
 
-  // ---- 1. top-k (one warp per token) or load of the given ids
-  if (p.logits != nullptr) {
-    const int per = (p.E + 31) >> 5;    // candidates per lane, <= 16
-    for (int t = warp; t < p.T; t += kRouteWarps) {
-      float v[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int e = lane + 32 * j;
-        float x = (j < per && e < p.E) ? p.logits[static_cast<size_t>(t) * p.E + e] : -INFINITY;
-        v[j] = (x == x) ? x : -INFINITY;   // NaN never wins
-      }
-      uint32_t taken = 0;
-      float my_val = 0.f;
-      int my_id = 0;
-      for (int r = 0; r < p.k; ++r) {
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int e = lane + 32 * j;
-          if (j < per && e < p.E && !((taken >> j) & 1u) && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-          if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-        }
-        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-        if (lane == r) { my_val = bv; my_id = bi; }
-      }
-      const float top = __shfl_sync(0xffffffffu, my_val, 0);
-      float ex = (lane < p.k) ? expf(my_val - top) : 0.f;
-      float sum = ex;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      if (lane < p.k) {
-        const float w = ex / sum;
-        p.ids_out[t * p.k + lane] = my_id;
-        p.wts_out[t * p.k + lane] = w;
-        const int le = my_id - p.local_start;
-        rexp[t * p.kk + lane] = (le >= 0 && le < p.local_count) ? le : -1;
-      }
-    }
-  } else {
-    for (int i = tid; i < p.T * p.k; i += kRouteThreads) {
-      const int t = i / p.k, s = i - t * p.k;
-      const int le = p.ids_in[i] - p.local_start;
-      rexp[t * p.kk + s] = (le >= 0 && le < p.local_count) ? le : -1;
-    }
+  // ---- 1. the routes' expert slots (global ids outside the local range are skipped)
+  for (int i = tid; i < p.T * p.k; i += kRouteThreads) {
+    const int t = i / p.k, sl = i - t * p.k;
+    const int le = p.ids_in[i] - p.local_start;
+    rexp[t * p.kk + sl] = (le >= 0 && le < p.local_count) ? le : -1;
   }
   if (p.has_shared)
     for (int t = tid; t < p.T; t += kRouteThreads)
       rexp[t * p.kk + p.k] = (t >= p.own_t0 && t < p.own_t1) ? p.local_count : -1;
   __syncthreads();
+  OKC_ROUTE_MARK(1)
 
   // ---- 2. per-warp histograms over contiguous chunks of the route list
   const int chunk = ((R + kRouteWarps - 1) / kRouteWarps + 31) & ~31;
@@ -114,6 +146,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     p.counts[e] = run;
   }
   __syncthreads();
+  OKC_ROUTE_MARK(2)
   // ---- 3. offsets (exclusive scan over slots) by warp 0
   if (warp == 0) {
     const int per = (p.slots + 31) >> 5;
@@ -137,6 +170,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
   }
   __syncthreads();
 
+  OKC_ROUTE_MARK(3)
   // ---- 4. stable positions: offset of the expert + routes of that expert before this one
   for (int b = 0; b < chunk; b += 32) {
     const int i = r0 + b + lane;
@@ -147,7 +181,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
         const int q = offs[e] + whist[warp * p.slots + e] + __popc(m & ((1u << lane) - 1u));
         const int t = i / p.kk, s = i - t * p.kk;
         float w = 1.0f;
-        if (s < p.k) w = (p.logits != nullptr) ? p.wts_out[t * p.k + s] : p.wts_in[t * p.k + s];
+        if (s < p.k) w = p.wts_in[t * p.k + s];
         p.pos[i] = q;
         p.sorted[q] = i;
         p.wsorted[q] = w;
@@ -160,6 +194,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     __syncwarp();
   }
 
+  OKC_ROUTE_MARK(4)
   // ---- 5. work items: experts by load descending (ties by id), cut into runs of <= chunk_rows rows
   int active = 0;
   for (int e = tid; e < p.slots; e += kRouteThreads) {
@@ -176,6 +211,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
   }
   if (active) atomicAdd(&s_nact, active);
   __syncthreads();
+  OKC_ROUTE_MARK(5)
   const int n_active = s_nact;
   if (warp == 0) {
     const int per = (n_active + 31) >> 5;
@@ -215,6 +251,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
       p.items[it] = make_int4(e, offs[e] + c0, n, npad);
     }
   }
+  OKC_ROUTE_MARK(6)
 }
 
 // xg[pos] = hidden[token of the route at pos]: rows of the gate_up GEMM's token operand in expert order.
@@ -272,8 +309,19 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
   const size_t smem = route_smem_bytes(p.T * p.kk, p.slots);
   cudaError_t e = cudaFuncSetAttribute(okc_route_sort, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  okc_route_sort<<<1, kRouteThreads, smem, stream>>>(p);
-  return cudaGetLastError();
+  if (p.logits != nullptr) {
+    // the router proper: ids / weights of every token, then the sort below reads them back
+    const dim3 grid((p.T + 7) / 8), block(256);
+    if (p.E <= 128) okc_route_topk<4><<<grid, block, 0, stream>>>(p.logits, p.T, p.E, p.k, p.ids_out, p.wts_out);
+    else if (p.E <= 256) okc_route_topk<8><<<grid, block, 0, stream>>>(p.logits, p.T, p.E, p.k, p.ids_out, p.wts_out);
+    else okc_route_topk<16><<<grid, block, 0, stream>>>(p.logits, p.T, p.E, p.k, p.ids_out, p.wts_out);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    RouteParams q = p;
+    q.logits = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
+    return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, q);
+  }
+  return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, p);
 }
 
 cudaError_t launch_gather(const void* hidden, int64_t stride, int32_t* meta, const int32_t* sorted, int kk,
