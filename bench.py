@@ -351,6 +351,27 @@ def run_gpu(args):
     bytes_per_seed = [synth.algorithmic_bytes(wl, n, tokens if world == 1 else tokens, shared=bool(wl.shared_inter))
                       for n in touched]
 
+    # ---- roofline of the dominant kernel (the grouped-GEMM launch): CUDA events around each kernel of the
+    # expert phase, taken before the timed region (right after a long back-to-back run the same kernels
+    # were measured up to 5 % slower between their events than they run inside the replayed step)
+    phases = {"gather": [], "gemm": [], "combine": [], "total": []}
+    prof_out = torch.empty((tokens, wl.hidden), dtype=torch.float32 if world > 1 else torch.bfloat16, device=dev)
+    n_prof = 15
+    gate_up_bytes = []
+    for i in range(n_prof + 2):
+        j = i % len(SEEDS)
+        h, lg = inputs[j]
+        okc.route(lg, state, own_tokens=(t0, t1))
+        flush_l2()
+        torch.cuda.synchronize()
+        ms = okc.experts_profiled(h, state, prof_out)
+        if i >= 2:
+            for k in phases:
+                phases[k].append(ms[k])
+            n_exp = touched[j] + (1 if wl.shared_inter else 0)
+            # weight stream of both GEMMs (4 bits + 1/16 scale byte per element) + the gathered token rows
+            gate_up_bytes.append(n_exp * 3 * wl.inter * wl.hidden * 9 // 16 + tokens * wl.top_k * wl.hidden * 2)
+
     # the clock sampler starts before the warm-up; samples from before the timed region are dropped
     # when NVML is read in-process (the nvidia-smi fallback keeps them: it is slow to start, and they
     # too were taken under this workload)
@@ -395,26 +416,9 @@ def run_gpu(args):
     ms_per_step = total_ms / args.steps
     value = step_bytes / (total_ms * 1e-3) / 1e9
 
-    # ---- roofline of the dominant kernel (the grouped-GEMM launch), CUDA events around each kernel
+    # ---- roofline figures from the per-kernel events taken before the timed region
     roof = None
-    phases = {"gather": [], "gemm": [], "combine": [], "total": []}
-    prof_out = torch.empty((tokens, wl.hidden), dtype=torch.float32 if world > 1 else torch.bfloat16, device=dev)
-    n_prof = max(3, min(args.steps, 12))
-    gate_up_bytes = []
-    for i in range(n_prof + 2):
-        j = i % len(SEEDS)
-        h, lg = inputs[j]
-        okc.route(lg, state, own_tokens=(t0, t1))
-        flush_l2()
-        torch.cuda.synchronize()
-        ms = okc.experts_profiled(h, state, prof_out)
-        if i >= 2:
-            for k in phases:
-                phases[k].append(ms[k])
-            n_exp = touched[j] + (1 if wl.shared_inter else 0)
-            # weight stream of both GEMMs (4 bits + 1/16 scale byte per element) + the gathered token rows
-            gate_up_bytes.append(n_exp * 3 * wl.inter * wl.hidden * 9 // 16 + tokens * wl.top_k * wl.hidden * 2)
-    gu_ms = statistics.mean(phases["gemm"])
+    gu_ms = statistics.median(phases["gemm"])
     achieved = statistics.mean(gate_up_bytes) / (gu_ms * 1e-3) / 1e9
     # DRAM traffic of one launch from the ncu capture summarised under profiles/
     # (dram__bytes_read.sum + dram__bytes_write.sum at 115 touched experts of configuration 2),
@@ -424,8 +428,9 @@ def run_gpu(args):
         traffic = NCU_TRAFFIC_C2_115 / 115.0 * statistics.mean(touched)
     roof = {"kernel": "okc_moe_gemm (gate_up + SiLU*mul units, then down units, one launch)", "bound": "hbm", "achieved": achieved, "peak": peak_gbs,
             "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": traffic,
-            "kernel_ms": {k: statistics.mean(v) for k, v in phases.items()},
+            "kernel_ms": {k: statistics.median(v) for k, v in phases.items()},
             "step_frac_of_peak": value / (peak_gbs * world)}
+
 
     # ---- end to end through the public API with host buffers
     e2e = None

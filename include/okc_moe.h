@@ -195,6 +195,15 @@ int okc_ep_views(const okc_ep_comm* comm, void** hidden_all, void** logits_all, 
 int okc_ep_gather_tokens(const okc_ep_comm* comm, const void* hidden_own, int64_t hidden_stride,
                          const float* logits_own, okc_stream_t stream);
 int okc_ep_reduce_scatter(const okc_ep_comm* comm, void* out_bf16, okc_stream_t stream);
+/* okc_moe_experts for one rank of the expert-parallel layer with its last kernel replaced: the
+ * per-token combine and okc_ep_reduce_scatter in one kernel (a rank's partial sums of its own rows
+ * stay in registers).  hidden = okc_ep_views' hidden_all, T = comm->tokens; plans with post_norm are
+ * refused (OKC_ERR_BAD_PLAN: use okc_moe_experts + okc_ep_reduce_scatter).  Detail of a wait that
+ * ran out: 0x300 + rank. */
+int okc_moe_experts_ep(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                       const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,
+                       int T, void* workspace, const okc_ep_comm* comm, void* out_bf16,
+                       okc_stream_t stream);
 /* Synchronises `stream`; returns the status kept in this rank's buffer and clears it. */
 int okc_ep_read_status(const okc_ep_comm* comm, okc_stream_t stream, int32_t* detail);
 

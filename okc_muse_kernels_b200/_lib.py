@@ -71,6 +71,7 @@ SIGNATURES = {
     "okc_ep_views": (C.c_int, [_COMM, C.POINTER(_P), C.POINTER(_P), C.POINTER(_P)]),
     "okc_ep_gather_tokens": (C.c_int, [_COMM, _P, C.c_int64, _P, _P]),
     "okc_ep_reduce_scatter": (C.c_int, [_COMM, _P, _P]),
+    "okc_moe_experts_ep": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _COMM, _P, _P]),
     "okc_ep_read_status": (C.c_int, [_COMM, _P, C.POINTER(C.c_int32)]),
 }
 

@@ -208,9 +208,12 @@ int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weig
 
 // Launches the four kernels of the expert phase; `ev`, when given, holds five events recorded
 // before / between / after them (gather, gate_up, down, combine).
+static bool ep_params(const okc_ep_comm* c, EpParams& p);
+
 static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
                         const float* gs2, const void* hidden, int64_t hidden_stride, int T, const void* post_norm_w,
-                        void* workspace, void* out, int out_f32, cudaStream_t stream, cudaEvent_t* ev) {
+                        void* workspace, void* out, int out_f32, cudaStream_t stream, cudaEvent_t* ev,
+                        const EpParams* ep = nullptr) {
   Geometry g;
   if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
   if (!packed_w13 || !packed_w2 || !gs13 || !gs2 || !hidden || !workspace || !out) return OKC_ERR_BAD_ARG;
@@ -264,7 +267,12 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   CombineParams c;
   c.y = w.y; c.pos = w.pos; c.wsorted = w.wsorted; c.post_w = static_cast<const uint16_t*>(post_norm_w);
   c.out = out; c.kk = g.kk; c.H = g.H; c.out_f32 = out_f32 ? 1 : 0;
-  if (launch_combine(c, T, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  if (ep) {
+    // the combine and the reduce-scatter over the ranks in one kernel
+    if (launch_ep_combine_reduce(*ep, c, stream) != cudaSuccess) return OKC_ERR_CUDA;
+  } else if (launch_combine(c, T, stream) != cudaSuccess) {
+    return OKC_ERR_CUDA;
+  }
   if (ev && cudaEventRecord(ev[3], stream) != cudaSuccess) return OKC_ERR_CUDA;
   return OKC_OK;
 }
@@ -405,6 +413,19 @@ int okc_ep_reduce_scatter(const okc_ep_comm* comm, void* out_bf16, okc_stream_t 
   if (!out_bf16 || !aligned(out_bf16, 8)) return OKC_ERR_BAD_ARG;
   p.out = static_cast<uint16_t*>(out_bf16);
   return launch_ep_reduce(p, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+int okc_moe_experts_ep(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
+                       const float* gs2, const void* hidden, int64_t hidden_stride, int T, void* workspace,
+                       const okc_ep_comm* comm, void* out_bf16, okc_stream_t stream) {
+  EpParams p;
+  if (!ep_params(comm, p)) return OKC_ERR_BAD_ARG;
+  if (!plan || plan->post_norm != 0) return OKC_ERR_BAD_PLAN;   // the post-expert norm needs whole rows
+  if (T != p.tokens || plan->hidden != p.H || !out_bf16 || !aligned(out_bf16, 8)) return OKC_ERR_BAD_ARG;
+  p.out = static_cast<uint16_t*>(out_bf16);
+  // `out` of the unfused path is not written; the partial sums go to the exchange buffer
+  return experts_impl(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, T, nullptr, workspace,
+                      p.peer[p.rank] + p.off_partial, 1, reinterpret_cast<cudaStream_t>(stream), nullptr, &p);
 }
 
 int okc_ep_read_status(const okc_ep_comm* comm, okc_stream_t stream_, int32_t* detail) {

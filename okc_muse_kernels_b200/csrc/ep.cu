@@ -9,6 +9,8 @@
 //                 for the flags of the others, reads its own token rows of every rank's FP32 partial
 //                 sums (rank order, so the sum is deterministic) and writes them as bf16: a
 //                 reduce-scatter and the cast in one kernel.
+//   combine_reduce: the per-token combine of the local experts' outputs and pull_reduce in one
+//                 kernel (the partial sums of a rank's own rows never leave its registers).
 //
 // The reference has no counterpart: its expert all-reduce is not run (muse_moe_w4a16/baseline.py:8).
 //
@@ -162,6 +164,77 @@ __global__ void __launch_bounds__(256) okc_ep_pull_reduce(const EpParams p) {
   }
 }
 
+// The per-token combine of the local experts' outputs and the reduce-scatter in one kernel.
+// grid (H / 1024, T); the rows this rank owns are the last block rows, so that by the time their
+// CTAs wait for the other ranks, every CTA that only has to publish a partial row has been started.
+//   every row t:   acc = sum over the token's local routes (slot order) of y[t * kk + slot]
+//   row of a peer: store acc into this rank's partial sums (the owner will load it)
+//   own row:       wait until every rank has published its partial sums, add them in rank order
+//                  (this rank's acc in its place), round once to bf16
+// The CTA that is last to finish the first part raises this rank's flag on every rank.
+__global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, const CombineParams c) {
+  griddep_wait();    // y comes from the GEMM launch before
+  uint8_t* mine = p.peer[p.rank];
+  int32_t* ctrl = ctrl_of(mine);
+  const int tb = p.tokens / p.world;
+  const int own_t0 = p.rank * tb, own_t1 = own_t0 + tb;
+  const int32_t seq = ctrl[kEpCtrlSeqRs] + 1;   // changed only after every CTA has read it
+  int t = static_cast<int>(blockIdx.y) + own_t1;
+  if (t >= p.tokens) t -= p.tokens;
+  const bool own = t >= own_t0 && t < own_t1;
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const bool live = col < p.H;
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    for (int s = 0; s < c.kk; ++s) {
+      if (c.pos[t * c.kk + s] < 0) continue;   // uniform over the block
+      const float4 a = *reinterpret_cast<const float4*>(c.y + static_cast<size_t>(t * c.kk + s) * p.H + col);
+      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    }
+    if (!own)
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(mine + p.off_partial) + static_cast<size_t>(t) * p.H + col) = acc;
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    const int total = gridDim.x * gridDim.y;
+    s_last = (atomicAdd(&ctrl[kEpCtrlDoneRs], 1) == total - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    // every CTA of this rank has published (and fenced) its rows
+    __threadfence_system();
+    if (threadIdx.x < p.world) st_release_sys(flags_rs_of(p.peer[threadIdx.x]) + p.rank, seq);
+    if (threadIdx.x == 0) {
+      ctrl[kEpCtrlDoneRs] = 0;
+      ctrl[kEpCtrlSeqRs] = seq;
+    }
+  }
+  if (!own) return;
+  if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+    if (!wait_flag(flags_rs_of(mine) + threadIdx.x, seq)) {
+      atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
+      atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x300 | threadIdx.x);
+    }
+  }
+  __syncthreads();
+  if (!live) return;
+  const size_t off = static_cast<size_t>(t) * p.H + col;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < p.world; ++r) {       // rank order: the same sum on every run
+    float4 v = acc;
+    if (r != p.rank) v = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r] + p.off_partial) + off);
+    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+  }
+  __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&lo);
+  o.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p.out + static_cast<size_t>(t - own_t0) * p.H + col) = o;
+}
+
 cudaError_t launch_ep_push(const EpParams& p, cudaStream_t stream) {
   const int tb = p.tokens / p.world;
   int gx = 128 / p.world;
@@ -175,6 +248,10 @@ cudaError_t launch_ep_reduce(const EpParams& p, cudaStream_t stream) {
   const int tb = p.tokens / p.world;
   okc_ep_pull_reduce<<<dim3((p.H + 1023) / 1024, tb), 256, 0, stream>>>(p);
   return cudaGetLastError();
+}
+
+cudaError_t launch_ep_combine_reduce(const EpParams& p, const CombineParams& c, cudaStream_t stream) {
+  return launch_kernel(okc_ep_combine_reduce, dim3((p.H + 1023) / 1024, p.tokens), dim3(256), 0, stream, true, p, c);
 }
 
 }  // namespace okc

@@ -95,6 +95,7 @@ struct CombineParams {
   int kk, H, out_f32;
 };
 cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream);
+cudaError_t launch_ep_combine_reduce(const EpParams& p, const CombineParams& c, cudaStream_t stream);
 
 cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t stream);
 cudaError_t launch_wait_timeout_probe(int32_t* status, cudaStream_t stream);

@@ -18,7 +18,8 @@ Two implementations of steps 1 and 3 + 4:
   * ``exchange="peer"``: this library's own kernels over peer memory (``PeerExchange``): every rank
     maps every rank's exchange buffer; one kernel stores the rank's token block into all buffers and
     waits for the others' (step 1), one kernel pulls the rank's rows of all partial sums, adds them
-    in rank order and rounds once (steps 3 + 4).  Two launches instead of three collectives and a cast.
+    in rank order and rounds once (steps 3 + 4) -- by default fused with the per-token combine of the
+    local experts' outputs (``fuse_combine``).  Two launches instead of three collectives and a cast.
   * ``exchange="nccl"``: ``all_gather_into_tensor`` x 2, ``reduce_scatter_tensor``, the cast kernel.
     Also what the CPU test harness (gloo) runs.
 """
@@ -32,7 +33,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .moe import MoEPlan, cast_bf16, moe_step, prepare
+from .moe import MoEPlan, cast_bf16, experts_ep, moe_step, prepare, route
 
 
 def shard_plan(hidden: int, inter: int, n_experts: int, top_k: int, world: int, rank: int, max_tokens: int,
@@ -142,7 +143,7 @@ class ExpertParallelMoE:
 
     def __init__(self, plan: MoEPlan, tokens: int, weights: dict | None = None, group=None,
                  local_step: Callable | None = None, cast: Callable | None = None,
-                 device: torch.device | str | None = None, exchange: str = "nccl"):
+                 device: torch.device | str | None = None, exchange: str = "nccl", fuse_combine: bool = True):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -169,6 +170,9 @@ class ExpertParallelMoE:
         if exchange == "peer" and local_step is not None:
             raise ValueError("the peer-memory exchange runs on GPUs only")
         self.exchange = exchange
+        # peer exchange: the combine and the reduce-scatter as one kernel (not with the post-expert
+        # norm, which needs whole rows before the sum)
+        self.fuse_combine = bool(fuse_combine and exchange == "peer" and not plan.post_norm)
         self.peer = None
         if exchange == "peer":
             self.peer = PeerExchange(tokens, plan.hidden, plan.n_experts, group=group, device=device)
@@ -188,8 +192,12 @@ class ExpertParallelMoE:
         of the layer output).  The returned tensor is reused by the next call."""
         if self.peer is not None:
             self.peer.gather_tokens(hidden_own, logits_own)
-            self._local_step(self.hidden_all, self.logits_all, self.own, self.partial)
-            self.peer.reduce_scatter(self.out)
+            if self.fuse_combine:
+                route(self.logits_all, self.state, own_tokens=self.own)
+                experts_ep(self.hidden_all, self.state, self.peer.comm, self.out)
+            else:
+                self._local_step(self.hidden_all, self.logits_all, self.own, self.partial)
+                self.peer.reduce_scatter(self.out)
             return self.out
         dist.all_gather_into_tensor(self.hidden_all, hidden_own.contiguous(), group=self.group)
         dist.all_gather_into_tensor(self.logits_all, logits_own.contiguous(), group=self.group)

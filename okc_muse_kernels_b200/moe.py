@@ -20,7 +20,7 @@ from . import _lib
 from ._lib import OkcError, Plan, Sizes
 
 __all__ = ["MoEPlan", "prepare", "kernel_fn", "moe_step", "route", "sorted_routes", "unpack_bf16", "read_status",
-           "experts_profiled", "cast_bf16", "OkcError"]
+           "experts_profiled", "experts_ep", "cast_bf16", "OkcError"]
 
 
 @dataclass(frozen=True)
@@ -166,6 +166,21 @@ def _experts(hidden, stride, T, state, out, out_f32):
         state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, T,
         _ptr(state["post_norm_w"]), state["workspace"].data_ptr(), out.data_ptr(), int(out_f32), _stream()),
         "okc_moe_experts")
+
+
+def experts_ep(hidden_all: torch.Tensor, state: dict, comm, out: torch.Tensor) -> torch.Tensor:
+    """One rank's expert phase of the expert-parallel layer on routes already sorted into the state
+    (``route`` was called on all tokens), ending in the fused combine + reduce-scatter kernel:
+    ``out`` bf16 [T/world, H] receives this rank's rows of the layer output.  ``comm`` is the
+    ``okc_ep_comm`` of a ``PeerExchange``; ``hidden_all`` its gathered token rows."""
+    plan: MoEPlan = state["plan"]
+    hidden, stride = _check_hidden(hidden_all, plan)
+    _need_cuda(out)
+    _lib.check(_lib.lib().okc_moe_experts_ep(
+        C.byref(plan.c_plan()), state["packed_w13"].data_ptr(), state["packed_w2"].data_ptr(),
+        state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, hidden.shape[0],
+        state["workspace"].data_ptr(), C.byref(comm), out.data_ptr(), _stream()), "okc_moe_experts_ep")
+    return out
 
 
 def kernel_fn(data: dict, state: dict, *, out_f32: bool = False, own_tokens=None) -> torch.Tensor:

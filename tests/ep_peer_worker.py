@@ -26,7 +26,8 @@ def main():
     w = synth.make_weights(wl, seed=21, device=dev)             # the whole layer, the same bits on every rank
     plan = ep.shard_plan(H, I, E, K, world, rank, max_tokens=max(T, 16), shared_inter=I)
     mine = synth.make_weights(wl, seed=21, device=dev, n_experts=plan.local_count, first_expert=plan.local_start)
-    peer = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer")
+    peer = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer")                # fused combine + reduce
+    split = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer", fuse_combine=False)
     nccl = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="nccl")
     t0, t1 = peer.own
     wn = synth.to_numpy_weights(w)
@@ -37,8 +38,12 @@ def main():
         hidden, logits = synth.make_inputs(wl, seed=100 + step, device=dev)
         a = peer.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
         b = nccl.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
+        c = split.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
         rc, detail = peer.peer.read_status()
         ok &= rc == 0
+        rc, detail = split.peer.read_status()
+        ok &= rc == 0
+        ok &= bool(torch.equal(a, c))                           # same sums in the same order
         if world == 2:
             ok &= bool(torch.equal(a, b))                       # two addends: the order cannot matter
         ok &= bool(torch.allclose(a.float(), b.float(), rtol=2 ** -7, atol=1e-5))
