@@ -20,7 +20,7 @@ from . import _lib
 from ._lib import OkcError, Plan, Sizes
 
 __all__ = ["MoEPlan", "prepare", "kernel_fn", "moe_step", "route", "sorted_routes", "unpack_bf16", "read_status",
-           "experts_profiled", "experts_ep", "cast_bf16", "OkcError"]
+           "experts_profiled", "experts_ep", "cast_bf16", "HostStep", "OkcError"]
 
 
 @dataclass(frozen=True)
@@ -166,6 +166,48 @@ def _experts(hidden, stride, T, state, out, out_f32):
         state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, T,
         _ptr(state["post_norm_w"]), state["workspace"].data_ptr(), out.data_ptr(), int(out_f32), _stream()),
         "okc_moe_experts")
+
+
+class HostStep:
+    """A step whose inputs and output live in pinned host memory, captured once in a CUDA graph:
+    host -> device copies of the token rows and router logits, the step, device -> host copy of the
+    result.  ``replay()`` enqueues all of it with one launch on the current stream; the caller
+    synchronises before reading ``out_host`` and rewrites ``hidden_host`` / ``logits_host`` in place
+    between replays.  The reference's harness times its ``kernel_fn`` the same way, graph-captured
+    (muse_moe_w4a16/bench.py:36-56).
+
+    ``step(d_hidden, d_logits) -> device tensor`` defaults to ``moe_step`` on ``state``; an
+    expert-parallel layer passes its own ``step``."""
+
+    def __init__(self, state: dict, hidden_host: torch.Tensor, logits_host: torch.Tensor, out_host: torch.Tensor,
+                 step=None):
+        for t in (hidden_host, logits_host, out_host):
+            if t.is_cuda or not t.is_pinned():
+                raise ValueError("HostStep wants pinned host tensors")
+        dev = state["workspace"].device
+        self.hidden_host, self.logits_host, self.out_host = hidden_host, logits_host, out_host
+        self.d_hidden = torch.empty(hidden_host.shape, dtype=hidden_host.dtype, device=dev)
+        self.d_logits = torch.empty(logits_host.shape, dtype=logits_host.dtype, device=dev)
+        if step is None:
+            d_out = torch.empty((hidden_host.shape[0], state["plan"].hidden), dtype=torch.bfloat16, device=dev)
+
+            def step(h, lg):
+                return moe_step(h, lg, state, out=d_out)
+        self._step = step
+        self._run()                      # eager once: kernel attributes, lazy initialisation
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._run()
+
+    def _run(self):
+        self.d_hidden.copy_(self.hidden_host, non_blocking=True)
+        self.d_logits.copy_(self.logits_host, non_blocking=True)
+        out = self._step(self.d_hidden, self.d_logits)
+        self.out_host.copy_(out, non_blocking=True)
+
+    def replay(self) -> None:
+        self.graph.replay()
 
 
 def experts_ep(hidden_all: torch.Tensor, state: dict, comm, out: torch.Tensor) -> torch.Tensor:

@@ -307,6 +307,28 @@ def test_experts_run_again_on_the_same_routes():
         assert torch.equal(out, want)
 
 
+def test_host_step_graph_replays_from_pinned_memory():
+    """okc.HostStep: host -> device copies, the step and the copy back in one captured graph; new inputs
+    written into the pinned buffers are picked up by the next replay."""
+    dev = _dev()
+    wl = synth.Workload("hs", 12, 512, 256, 16, 4)
+    w = synth.make_weights(wl, seed=9, device=dev)
+    state = okc.prepare(w, okc.MoEPlan(hidden=512, inter=256, n_experts=16, top_k=4, max_tokens=16))
+    h1, l1 = synth.make_inputs(wl, seed=10, device=dev)
+    h2, l2 = synth.make_inputs(wl, seed=11, device=dev)
+    hh, ll = h1.cpu().pin_memory(), l1.cpu().pin_memory()
+    out_host = torch.empty((12, 512), dtype=torch.bfloat16).pin_memory()
+    step = okc.HostStep(state, hh, ll, out_host)
+    for h, lg in ((h1, l1), (h2, l2), (h1, l1)):
+        hh.copy_(h.cpu())
+        ll.copy_(lg.cpu())
+        step.replay()
+        torch.cuda.synchronize()
+        got = out_host.clone()
+        assert torch.equal(got, okc.moe_step(h, lg, state).cpu())
+    _status_ok(state)
+
+
 def test_zipf_routing_hot_expert_chunks():
     """Config 5's routing skew at a narrower width: one expert takes > 128 tokens, so its rows are cut
     into several work items."""
