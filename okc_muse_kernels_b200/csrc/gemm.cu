@@ -207,25 +207,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
         u.slot = wi.x; u.pos0 = wi.y; u.rows = wi.z; u.npad = wi.w; u.stages = pp.stages;
         ctrl->units[k] = u;
         mbar_arrive(bar_ufull + 8 * k);
-        if (u.phase == 1) {
-          // the token operand of a down unit is the gate_up output of its work item: wait until the
-          // four epilogue warps of each of the item's gate_up units have stored and published it
-          const int target = 4 * p.ph[0].pairs;
-          uint32_t spins = 0;
-          while (ld_acquire_gpu(p.done + u.item) < target) {
-            __nanosleep(100);
-            if ((++spins & 255u) == 0) {
-              if (*abort_flag != 0) { ok = false; break; }
-              if (spins >= (1u << 22)) { atomicCAS(const_cast<int*>(abort_flag), 0, kWaitProducerDone); ok = false; break; }
-            }
-          }
-          if (!ok) break;
-          fence_proxy_async();   // those stores were generic-proxy writes; the loads below are TMA
-        }
         const int mi = (u.npad == 16) ? 0 : 1;
         const uint8_t* src = pp.wpacked + static_cast<size_t>(u.slot) * pp.expert_bytes +
                              static_cast<size_t>(u.pair) * pp.stages * kStageBytes;
-        for (int s = 0; s < pp.stages; ++s) {
+        int s_begin = 0;
+        if (u.phase == 1) {
+          // The token operand of a down unit is the gate_up output of its work item: all four
+          // epilogue warps of each of the item's gate_up units must have stored and published it.
+          const int target = 4 * p.ph[0].pairs;
+          if (ld_acquire_gpu(p.done + u.item) < target) {
+            // Not yet.  The weights do not depend on it: start their copies for as many stages as the
+            // ring holds, wait, then send the token tiles after them (a stage's barrier completes
+            // when both parts have arrived).
+            const int pre = pp.stages < NS ? pp.stages : NS;
+            int st2 = st, sent = 0;
+            uint32_t ph2 = ph;
+            for (int s = 0; s < pre; ++s) {
+              if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st2, ph2 ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
+              mbar_expect_tx(bar_full + 8 * st2, kStageBytes + u.npad * 512);
+              bulk_g2s_hint(smem0 + st2 * stage_bytes, src + static_cast<size_t>(s) * kStageBytes, kStageBytes, bar_full + 8 * st2, pol);
+              ++sent;
+              if (++st2 == NS) { st2 = 0; ph2 ^= 1; }
+            }
+            uint32_t spins = 0;
+            while (ok && ld_acquire_gpu(p.done + u.item) < target) {
+              __nanosleep(100);
+              if ((++spins & 255u) == 0) {
+                if (*abort_flag != 0) { ok = false; break; }
+                if (spins >= (1u << 22)) { atomicCAS(const_cast<int*>(abort_flag), 0, kWaitProducerDone); ok = false; break; }
+              }
+            }
+            fence_proxy_async();   // those stores were generic-proxy writes; the loads below are TMA
+            // (also when giving up: the stages whose weights are in flight get their token tiles, so
+            // that their barriers complete and the CTA can wait for its copies before it retires)
+            for (int s = 0; s < sent; ++s) {
+              const uint32_t dst = smem0 + st * stage_bytes;
+#pragma unroll
+              for (int kb = 0; kb < 4; ++kb)
+                tma_2d_g2s(dst + kStageBytes + kb * u.npad * 128, &pp.bmap[mi], s * kStageK + kb * 64, u.pos0, bar_full + 8 * st);
+              ++issued;
+              if (++st == NS) { st = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            s_begin = pre;
+          } else {
+            fence_proxy_async();
+          }
+        }
+        for (int s = s_begin; s < pp.stages; ++s) {
           if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
           const uint32_t bar = bar_full + 8 * st;
           const uint32_t dst = smem0 + st * stage_bytes;

@@ -73,6 +73,13 @@ def _need_cuda(*tensors: torch.Tensor) -> None:
             raise ValueError("okc_muse_kernels_b200 runs on CUDA tensors only (there is no CPU path)")
 
 
+def _need_gpu_visible(*tensors: torch.Tensor) -> None:
+    """CUDA tensors, or pinned host tensors (which the GPU reads and writes in place over PCIe)."""
+    for t in tensors:
+        if t is not None and not (t.is_cuda or t.is_pinned()):
+            raise ValueError("okc_muse_kernels_b200 wants CUDA tensors or pinned host tensors (there is no CPU path)")
+
+
 def _u8(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous().view(torch.uint8)
 
@@ -169,15 +176,18 @@ def _experts(hidden, stride, T, state, out, out_f32):
 
 
 class HostStep:
-    """A step whose inputs and output live in pinned host memory, captured once in a CUDA graph:
-    host -> device copies of the token rows and router logits, the step, device -> host copy of the
-    result.  ``replay()`` enqueues all of it with one launch on the current stream; the caller
-    synchronises before reading ``out_host`` and rewrites ``hidden_host`` / ``logits_host`` in place
-    between replays.  The reference's harness times its ``kernel_fn`` the same way, graph-captured
+    """A step whose inputs and output live in pinned host memory, captured once in a CUDA graph.
+    ``replay()`` enqueues all of it with one launch on the current stream; the caller synchronises
+    before reading ``out_host`` and rewrites ``hidden_host`` / ``logits_host`` in place between
+    replays.  The reference's harness times its ``kernel_fn`` the same way, graph-captured
     (muse_moe_w4a16/bench.py:36-56).
 
-    ``step(d_hidden, d_logits) -> device tensor`` defaults to ``moe_step`` on ``state``; an
-    expert-parallel layer passes its own ``step``."""
+    With the default step (``moe_step`` on ``state``) the graph has two branches: a copy engine
+    brings the token rows to the device while the router's top-k kernel reads the logits straight
+    from the pinned buffer and the routes are sorted; the branches join before the rows are
+    gathered, and the combine kernel stores the result straight into ``out_host``.  With a custom
+    ``step(d_hidden, d_logits) -> device tensor`` (an expert-parallel layer's) the graph is: copy
+    both inputs to the device, the step, copy the result back."""
 
     def __init__(self, state: dict, hidden_host: torch.Tensor, logits_host: torch.Tensor, out_host: torch.Tensor,
                  step=None):
@@ -185,26 +195,39 @@ class HostStep:
             if t.is_cuda or not t.is_pinned():
                 raise ValueError("HostStep wants pinned host tensors")
         dev = state["workspace"].device
+        self.state = state
         self.hidden_host, self.logits_host, self.out_host = hidden_host, logits_host, out_host
         self.d_hidden = torch.empty(hidden_host.shape, dtype=hidden_host.dtype, device=dev)
-        self.d_logits = torch.empty(logits_host.shape, dtype=logits_host.dtype, device=dev)
-        if step is None:
-            d_out = torch.empty((hidden_host.shape[0], state["plan"].hidden), dtype=torch.bfloat16, device=dev)
-
-            def step(h, lg):
-                return moe_step(h, lg, state, out=d_out)
         self._step = step
-        self._run()                      # eager once: kernel attributes, lazy initialisation
-        torch.cuda.synchronize(dev)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self._run()
+        if step is None:
+            self._side = torch.cuda.Stream(device=dev)
+            if out_host.dtype != torch.bfloat16 or not out_host.is_contiguous():
+                raise ValueError("out_host must be a contiguous bf16 tensor")
+        else:
+            self.d_logits = torch.empty(logits_host.shape, dtype=logits_host.dtype, device=dev)
+        with torch.cuda.device(dev):
+            self._run()                      # eager once: kernel attributes, lazy initialisation
+            torch.cuda.synchronize(dev)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._run()
 
     def _run(self):
-        self.d_hidden.copy_(self.hidden_host, non_blocking=True)
-        self.d_logits.copy_(self.logits_host, non_blocking=True)
-        out = self._step(self.d_hidden, self.d_logits)
-        self.out_host.copy_(out, non_blocking=True)
+        if self._step is not None:
+            self.d_hidden.copy_(self.hidden_host, non_blocking=True)
+            self.d_logits.copy_(self.logits_host, non_blocking=True)
+            out = self._step(self.d_hidden, self.d_logits)
+            self.out_host.copy_(out, non_blocking=True)
+            return
+        plan: MoEPlan = self.state["plan"]
+        cur = torch.cuda.current_stream()
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):
+            self.d_hidden.copy_(self.hidden_host, non_blocking=True)
+        route(self.logits_host, self.state)
+        cur.wait_stream(self._side)
+        hidden, stride = _check_hidden(self.d_hidden, plan)
+        _experts(hidden, stride, hidden.shape[0], self.state, self.out_host, False)
 
     def replay(self) -> None:
         self.graph.replay()
@@ -258,7 +281,7 @@ def route(router_logits: torch.Tensor, state: dict, *, own_tokens=None):
     """Softmax top-k routing + the token->expert sort into the state's workspace.  Returns views of
     the state's ``ids`` int32 [T, k] and ``wts`` f32 [T, k] buffers."""
     plan: MoEPlan = state["plan"]
-    _need_cuda(router_logits)
+    _need_gpu_visible(router_logits)      # a pinned host tensor is read by the top-k kernel in place
     if router_logits.dtype != torch.float32 or router_logits.dim() != 2 or router_logits.shape[1] != plan.n_experts:
         raise ValueError(f"router_logits must be f32 [T, {plan.n_experts}]")
     T = router_logits.shape[0]
