@@ -292,17 +292,36 @@ def run_gpu(args):
         # read (not write) a buffer larger than L2 so no dirty lines are left behind
         flush_sink.add_(flush.view(torch.int64)[::64].sum())
 
+    # --route-from-hidden (N = 1): the router logits are computed from the token rows inside the step
+    # (okc.moe_layer_step: hidden . router_w^T in FP32, then softmax top-k) instead of being an input
+    router_w = None
+    if args.route_from_hidden:
+        if world > 1:
+            raise SystemExit("--route-from-hidden is a single-GPU option")
+        gr = torch.Generator(device=dev).manual_seed(4242)
+        router_w = torch.randn((wl.n_experts, wl.hidden), generator=gr, device=dev) * (wl.hidden ** -0.5)
+
+    def one_step(h, lg, o):
+        if router_w is not None:
+            return okc.moe_layer_step(h, router_w, state, out=o)
+        return okc.moe_step(h, lg, state, out=o)
+
+    def do_route(h, lg):
+        if router_w is not None:
+            return okc.route_hidden(h, router_w, state)
+        return okc.route(lg, state, own_tokens=(t0, t1))
+
     # ---- the step: graph replay at N = 1, eager collectives + kernels at N > 1
     outs = [torch.empty((tokens, wl.hidden), dtype=torch.bfloat16, device=dev) for _ in SEEDS]
     graphs = []
     if world == 1:
         for (h, lg), o in zip(inputs, outs):
-            okc.moe_step(h, lg, state, out=o)      # eager warm-up (sets kernel attributes)
+            one_step(h, lg, o)                     # eager warm-up (sets kernel attributes)
         torch.cuda.synchronize()
         for (h, lg), o in zip(inputs, outs):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                okc.moe_step(h, lg, state, out=o)
+                one_step(h, lg, o)
             graphs.append(g)
 
     exch = "" if world == 1 else ("peer-memory exchange kernels" if layer.exchange == "peer" else "NCCL collectives")
@@ -346,7 +365,7 @@ def run_gpu(args):
     # touched experts per seed (this rank), for the algorithmic bytes
     touched = []
     for h, lg in inputs:
-        ids, _ = okc.route(lg, state, own_tokens=(t0, t1))
+        ids, _ = do_route(h, lg)
         touched.append(_touched(ids.cpu().numpy(), plan.local_start, plan.local_count))
     bytes_per_seed = [synth.algorithmic_bytes(wl, n, tokens if world == 1 else tokens, shared=bool(wl.shared_inter))
                       for n in touched]
@@ -361,7 +380,7 @@ def run_gpu(args):
     for i in range(n_prof + 2):
         j = i % len(SEEDS)
         h, lg = inputs[j]
-        okc.route(lg, state, own_tokens=(t0, t1))
+        do_route(h, lg)
         flush_l2()
         torch.cuda.synchronize()
         ms = okc.experts_profiled(h, state, prof_out)
@@ -434,7 +453,7 @@ def run_gpu(args):
 
     # ---- end to end through the public API with host buffers
     e2e = None
-    if True:
+    if router_w is None:      # (the end-to-end leg is the step with logits as a host input)
         # okc.HostStep: pinned host inputs -> device, the step, result -> pinned host memory, captured
         # once per routing seed in a CUDA graph (one launch per step); the host waits for every step
         host_out = torch.empty((t1 - t0, wl.hidden), dtype=torch.bfloat16).pin_memory()
@@ -499,6 +518,7 @@ def run_gpu(args):
                 "config": {"workload": _workload_name(wl, tokens, world),
                            "l2": "touched weights per step exceed L2 (126 MB) and a 256 MB buffer is read between timed steps",
                            "timing": "CUDA-graph replay per step" if world == 1 else ep_timing,
+                           "router": "logits = hidden . router_w^T computed inside the step" if router_w is not None else "logits given",
                            "touched_experts_per_seed": touched, "routing_seeds": list(SEEDS)},
                 "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
                 "gpu_launches": (_lib.lib().okc_moe_launches_per_step() + (0 if world == 1 else 2 if layer.exchange == "peer" else 1)) * args.steps,
@@ -527,6 +547,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "c1", "c2", "c4", "c5"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--route-from-hidden", action="store_true",
+                    help="N = 1: compute the router logits from the token rows inside the step (okc.moe_layer_step)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the all-gather / reduce-scatter through this library's peer-memory kernels or NCCL")
     ap.add_argument("--ep-graphs", type=int, default=1, choices=[0, 1],

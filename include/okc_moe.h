@@ -99,6 +99,28 @@ int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weig
                  int own_t0, int own_t1, void* workspace, okc_stream_t stream);
 
 /*
+ * The router of the reference's decode layer, fused with the step before it: the router logits
+ * `hidden . w^T` are computed from the token rows (FP32 multiply-adds, split over K; they never exist
+ * as a tensor) and go straight into the top-k.  Replaces `_router_split` + `_routing`
+ * (muse_decode_layer/layer.py:325-351, 374-414) and `route` (muse_decode_layer/reference.py:419-424).
+ *   mode 0: softmax top-k as okc_moe_route.
+ *   mode 1: scores = sigmoid(multiplier * logit); the top_k of scores + bias are chosen (ties to the
+ *           lowest id); weights = chosen scores / (their sum + 1e-15).
+ * w: f32 [E, H] (NULL: take `logits` f32 [T, E] instead and only apply the mode); bias: f32 [E] or NULL.
+ * With w: T <= 256, E a multiple of 16; the per-route output area of `workspace` is used as scratch.
+ * Then sorts the routes as okc_moe_route does.
+ */
+typedef struct okc_router {
+  const float* w;
+  const float* bias;
+  int32_t mode;
+  float multiplier;
+} okc_router;
+int okc_moe_route_hidden(const okc_moe_plan* plan, const okc_router* router, const void* hidden,
+                         int64_t hidden_stride, const float* logits, int T, int own_t0, int own_t1,
+                         int32_t* ids, float* weights, void* workspace, okc_stream_t stream);
+
+/*
  * The experts on the routes sorted into `workspace`: gather -> one persistent launch of the
  * gate_up GEMM + SiLU*mul units and the down GEMM (x routing weight, un-permuted) units, a down
  * unit starting as soon as the gate_up units of its own work item are done -> per-token combine.

@@ -43,6 +43,11 @@ class EpComm(C.Structure):
                 ("n_experts", C.c_int32), ("reserved", C.c_int32 * 3), ("peer", C.c_void_p * EP_MAX_RANKS)]
 
 
+class Router(C.Structure):
+    """okc_router"""
+    _fields_ = [("w", C.c_void_p), ("bias", C.c_void_p), ("mode", C.c_int32), ("multiplier", C.c_float)]
+
+
 _P = C.c_void_p
 _PLAN = C.POINTER(Plan)
 _COMM = C.POINTER(EpComm)
@@ -54,6 +59,7 @@ SIGNATURES = {
     "okc_moe_query": (C.c_int, [_PLAN, C.POINTER(Sizes)]),
     "okc_moe_repack": (C.c_int, [_PLAN, _P, _P, _P, _P, C.c_int, C.c_int, _P, _P, _P]),
     "okc_moe_route": (C.c_int, [_PLAN, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
+    "okc_moe_route_hidden": (C.c_int, [_PLAN, C.POINTER(Router), _P, C.c_int64, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
     "okc_moe_sort": (C.c_int, [_PLAN, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "okc_moe_experts": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P]),
     "okc_moe_experts_profiled": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P,

@@ -99,7 +99,8 @@ static Ws carve(void* workspace, const Geometry& g) {
 
 static int route_common(const okc_moe_plan* plan, const float* logits, const int32_t* ids_in, const float* wts_in,
                         int T, int own_t0, int own_t1, int32_t* ids_out, float* wts_out, void* workspace,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const okc_router* router = nullptr, const void* hidden = nullptr,
+                        int64_t hidden_stride = 0) {
   Geometry g;
   if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
   if (!workspace || !aligned(workspace, 256) || T <= 0 || T > plan->max_tokens) return OKC_ERR_BAD_ARG;
@@ -111,6 +112,26 @@ static int route_common(const okc_moe_plan* plan, const float* logits, const int
   p.T = T; p.E = plan->n_experts; p.k = plan->top_k; p.kk = g.kk; p.slots = g.slots;
   p.local_start = plan->local_start; p.local_count = plan->local_count; p.has_shared = plan->shared_inter ? 1 : 0;
   p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items; p.chunk_rows = chunk_rows_for(T, plan->top_k, plan->n_experts);
+  p.router_mode = 0; p.router_mult = 1.0f; p.router_bias = nullptr; p.router_w = nullptr; p.hidden = nullptr;
+  p.hidden_stride = 0; p.H = g.H; p.router_splits = 0; p.router_part = nullptr;
+  if (router) {
+    if (router->mode != 0 && router->mode != 1) return OKC_ERR_BAD_ARG;
+    p.router_mode = router->mode; p.router_mult = router->multiplier; p.router_bias = router->bias;
+    if (router->w) {
+      // logits from the token rows: split-K partial sums kept in the (not yet used) per-route output area
+      if (!hidden || !aligned(hidden, 16) || !aligned(router->w, 16) || hidden_stride < g.H || (hidden_stride % 8) != 0)
+        return OKC_ERR_BAD_ARG;
+      if (T > 256 || (p.E % 16) != 0) return OKC_ERR_BAD_PLAN;
+      long long splits = 148 / (p.E / 16);
+      const long long room = static_cast<long long>(g.kk) * g.H / p.E;   // [T * kk, H] floats hold `room` arrays [T, E]
+      if (splits > room) splits = room;
+      if (splits > g.H / 64) splits = g.H / 64;
+      if (splits > 16) splits = 16;
+      if (splits < 1) return OKC_ERR_BAD_PLAN;
+      p.router_w = router->w; p.hidden = static_cast<const uint16_t*>(hidden); p.hidden_stride = hidden_stride;
+      p.router_splits = static_cast<int>(splits); p.router_part = w.y;
+    }
+  }
   return launch_route(p, stream) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
 }
 
@@ -204,6 +225,16 @@ int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weig
   if (!ids || !weights) return OKC_ERR_BAD_ARG;
   return route_common(plan, nullptr, ids, weights, T, own_t0, own_t1, nullptr, nullptr, workspace,
                       reinterpret_cast<cudaStream_t>(stream));
+}
+
+int okc_moe_route_hidden(const okc_moe_plan* plan, const okc_router* router, const void* hidden, int64_t hidden_stride,
+                         const float* logits, int T, int own_t0, int own_t1, int32_t* ids, float* weights,
+                         void* workspace, okc_stream_t stream) {
+  if (!router || !ids || !weights) return OKC_ERR_BAD_ARG;
+  if ((router->w == nullptr) == (logits == nullptr)) return OKC_ERR_BAD_ARG;   // exactly one source of logits
+  if (!is_sm100()) return OKC_ERR_NO_DEVICE;
+  return route_common(plan, logits, nullptr, nullptr, T, own_t0, own_t1, ids, weights, workspace,
+                      reinterpret_cast<cudaStream_t>(stream), router, hidden, hidden_stride);
 }
 
 // Launches the four kernels of the expert phase; `ev`, when given, holds five events recorded

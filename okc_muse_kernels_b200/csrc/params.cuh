@@ -19,6 +19,16 @@ struct RouteParams {
   int32_t* pos;
   float* wsorted;
   int T, E, k, kk, slots, local_start, local_count, has_shared, own_t0, own_t1, max_items, chunk_rows;
+  // router: 0 = softmax top-k, 1 = sigmoid(mult * logit) + bias chooses, scores renormalised
+  int router_mode;
+  float router_mult;
+  const float* router_bias;       // f32 [E] or null
+  // logits from the token rows (null: `logits` is given)
+  const float* router_w;          // f32 [E, H]
+  const uint16_t* hidden;         // bf16 [T, hidden_stride]
+  int64_t hidden_stride;
+  int H, router_splits;
+  float* router_part;             // scratch f32 [router_splits, T, E]
 };
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
 cudaError_t launch_gather(const void* hidden, int64_t stride, int32_t* meta, const int32_t* sorted, int kk,

@@ -27,66 +27,145 @@ extern "C" int okc_moe_debug_route_profile(long long* host_out) {
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
-// Softmax top-k of the router logits, one warp per token, eight tokens per CTA (the tokens of a
-// step spread over many SMs: one CTA doing all of them is bound by its own instruction issue).
+// Router logits from the token rows: part[ks][t][e] = sum over the K range of split ks of
+// hidden[t][k] * w[e][k], FP32 multiply-adds in ascending k (bf16 -> f32 is exact).  The step before
+// the MoE path in the reference's layer (muse_decode_layer/layer.py:325-351, _router_split), fused
+// here with the routing: the logits never exist as a tensor, the top-k kernel adds the splits (in
+// split order) as it loads them.  grid (E / 16, splits), 256 threads: thread = (expert e0 + tid % 16,
+// tokens tid / 16 + 16 j).
+constexpr int kRtE = 16, kRtK = 64, kRtMaxT = 256;
+__global__ void __launch_bounds__(256) okc_router_partial(const uint16_t* __restrict__ hidden, int64_t stride,
+                                                          const float* __restrict__ w, int T, int H, int E, int kc,
+                                                          float* __restrict__ part) {
+  __shared__ uint32_t hs[kRtMaxT][kRtK / 2 + 1];   // bf16 pairs, rows padded against bank conflicts
+  __shared__ float ws[kRtE][kRtK + 1];
+  const int tid = threadIdx.x, e = tid & 15, tg = tid >> 4;
+  const int e0 = blockIdx.x * kRtE;
+  const int k_begin = blockIdx.y * kc, k_end = min(H, k_begin + kc);
+  float acc[kRtMaxT / 16];
+#pragma unroll
+  for (int j = 0; j < kRtMaxT / 16; ++j) acc[j] = 0.f;
+  for (int k0 = k_begin; k0 < k_end; k0 += kRtK) {
+    __syncthreads();
+    for (int i = tid; i < T * (kRtK / 8); i += 256) {          // 16-byte vectors of the token rows
+      const int t = i / (kRtK / 8), v = i - t * (kRtK / 8);
+      const uint4 x = *reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * stride + k0 + v * 8);
+      hs[t][v * 4 + 0] = x.x; hs[t][v * 4 + 1] = x.y; hs[t][v * 4 + 2] = x.z; hs[t][v * 4 + 3] = x.w;
+    }
+    {
+      const int r = tid >> 4, v = tid & 15;                       // 16 rows x 16 float4
+      const float4 x = *reinterpret_cast<const float4*>(w + static_cast<size_t>(e0 + r) * H + k0 + v * 4);
+      ws[r][v * 4 + 0] = x.x; ws[r][v * 4 + 1] = x.y; ws[r][v * 4 + 2] = x.z; ws[r][v * 4 + 3] = x.w;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k2 = 0; k2 < kRtK / 2; ++k2) {
+      const float w0 = ws[e][2 * k2], w1 = ws[e][2 * k2 + 1];
+#pragma unroll
+      for (int j = 0; j < kRtMaxT / 16; ++j) {
+        const int t = tg + 16 * j;
+        if (t < T) {
+          const uint32_t hv = hs[t][k2];
+          acc[j] = fmaf(__uint_as_float(hv << 16), w0, acc[j]);
+          acc[j] = fmaf(__uint_as_float(hv & 0xFFFF0000u), w1, acc[j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kRtMaxT / 16; ++j) {
+    const int t = tg + 16 * j;
+    if (t < T) part[(static_cast<size_t>(blockIdx.y) * T + t) * E + e0 + e] = acc[j];
+  }
+}
+
+// Top-k of the router, one warp per token, eight tokens per CTA (the tokens of a step spread over
+// many SMs: one CTA doing all of them is bound by its own instruction issue).
 // PER = candidates per lane (expert e sits in lane e % 32, slot e / 32).  Every lane keeps the best
 // of its untaken candidates; a round is a warp arg-max over those 32 values, after which only the
-// winner's lane looks for its next best.  Order: larger logit first, ties to the lower expert id,
+// winner's lane looks for its next best.  Order: larger key first, ties to the lower expert id,
 // NaN never wins.
+//   mode 0 (softmax):  key = logit; weights = softmax over the k selected logits.
+//   mode 1 (sigmoid):  score = sigmoid(mult * logit), key = score + bias[e]; weights = the selected
+//                      scores over (their sum + 1e-15)   (muse_decode_layer/reference.py:419-424,
+//                      variants/starter.py:177-182).
+// The logits are read from `logits` [T, E], or, with n_part > 0, as the sum in split order of the
+// n_part arrays [T, E] behind `logits` (the output of okc_router_partial).
 template <int PER>
-__global__ void __launch_bounds__(256) okc_route_topk(const float* __restrict__ logits, int T, int E, int k,
+__global__ void __launch_bounds__(256) okc_route_topk(const float* __restrict__ logits, int n_part, int T, int E, int k,
+                                                      int mode, float mult, const float* __restrict__ bias,
                                                       int32_t* __restrict__ ids_out, float* __restrict__ wts_out) {
+  griddep_wait();                // with n_part > 0 the logits come from the kernel launched just before
   griddep_launch_dependents();   // the sort kernel may set itself up; it waits for this grid to complete
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
-  float v[PER];
+  float v[PER];    // selection keys
+  float sc[PER];   // what the weights are made of (mode 1: the unbiased scores)
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int e = lane + 32 * j;
-    const float x = (e < E) ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    float x = -INFINITY;
+    if (e < E) {
+      x = logits[static_cast<size_t>(t) * E + e];
+      for (int s = 1; s < n_part; ++s) x += logits[(static_cast<size_t>(s) * T + t) * E + e];
+    }
+    if (mode == 1 && e < E) {
+      const float s1 = 1.0f / (1.0f + expf(-x * mult));
+      sc[j] = s1;
+      x = s1 + (bias != nullptr ? bias[e] : 0.f);
+    } else {
+      sc[j] = x;
+    }
     v[j] = (x == x) ? x : -INFINITY;
   }
   uint32_t taken = 0;
-  float bv = -INFINITY;
+  float bv = -INFINITY, bs = 0.f;
   int bi = 0x7fffffff;
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int e = lane + 32 * j;
-    if (e < E && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; }
+    if (e < E && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; bs = sc[j]; }
   }
   float my_val = 0.f;
   int my_id = 0;
   for (int r = 0; r < k; ++r) {
-    float wv = bv;
+    float wv = bv, wsc = bs;
     int wi = bi;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+      const float os = __shfl_xor_sync(0xffffffffu, wsc, o);
       const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
-      if (better(ov, oi, wv, wi)) { wv = ov; wi = oi; }
+      if (better(ov, oi, wv, wi)) { wv = ov; wi = oi; wsc = os; }
     }
-    if (lane == r) { my_val = wv; my_id = wi; }
+    if (lane == r) { my_val = wsc; my_id = wi; }
     if (wi == bi) {
       // this lane held the winner: next best of what it has left
       taken |= 1u << (wi >> 5);
       bv = -INFINITY;
+      bs = 0.f;
       bi = 0x7fffffff;
 #pragma unroll
       for (int j = 0; j < PER; ++j) {
         const int e = lane + 32 * j;
-        if (e < E && !((taken >> j) & 1u) && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; }
+        if (e < E && !((taken >> j) & 1u) && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; bs = sc[j]; }
       }
     }
   }
-  const float top = __shfl_sync(0xffffffffu, my_val, 0);
-  const float ex = (lane < k) ? expf(my_val - top) : 0.f;
+  float ex;
+  if (mode == 1) {
+    ex = (lane < k) ? my_val : 0.f;
+  } else {
+    const float top = __shfl_sync(0xffffffffu, my_val, 0);
+    ex = (lane < k) ? expf(my_val - top) : 0.f;
+  }
   float sum = ex;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   if (lane < k) {
     ids_out[t * k + lane] = my_id;
-    wts_out[t * k + lane] = ex / sum;
+    wts_out[t * k + lane] = (mode == 1) ? ex / (sum + 1e-15f) : ex / sum;
   }
 }
 
@@ -309,16 +388,33 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
   const size_t smem = route_smem_bytes(p.T * p.kk, p.slots);
   cudaError_t e = cudaFuncSetAttribute(okc_route_sort, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  if (p.logits != nullptr) {
+  if (p.logits != nullptr || p.router_w != nullptr) {
     // the router proper: ids / weights of every token, then the sort below reads them back
+    const float* lg = p.logits;
+    int n_part = 0;
+    if (p.router_w != nullptr) {
+      // logits = hidden . router_w^T as split-K partial sums in scratch; the top-k kernel adds the splits
+      n_part = p.router_splits;
+      const int kc = ((p.H / kRtK + n_part - 1) / n_part) * kRtK;
+      okc_router_partial<<<dim3(p.E / kRtE, n_part), 256, 0, stream>>>(p.hidden, p.hidden_stride, p.router_w, p.T, p.H, p.E,
+                                                                      kc, p.router_part);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      lg = p.router_part;
+    }
     const dim3 grid((p.T + 7) / 8), block(256);
-    if (p.E <= 128) okc_route_topk<4><<<grid, block, 0, stream>>>(p.logits, p.T, p.E, p.k, p.ids_out, p.wts_out);
-    else if (p.E <= 256) okc_route_topk<8><<<grid, block, 0, stream>>>(p.logits, p.T, p.E, p.k, p.ids_out, p.wts_out);
-    else okc_route_topk<16><<<grid, block, 0, stream>>>(p.logits, p.T, p.E, p.k, p.ids_out, p.wts_out);
-    e = cudaGetLastError();
+    if (p.E <= 128)
+      e = launch_kernel(okc_route_topk<4>, grid, block, 0, stream, n_part > 0, lg, n_part, p.T, p.E, p.k, p.router_mode,
+                        p.router_mult, p.router_bias, p.ids_out, p.wts_out);
+    else if (p.E <= 256)
+      e = launch_kernel(okc_route_topk<8>, grid, block, 0, stream, n_part > 0, lg, n_part, p.T, p.E, p.k, p.router_mode,
+                        p.router_mult, p.router_bias, p.ids_out, p.wts_out);
+    else
+      e = launch_kernel(okc_route_topk<16>, grid, block, 0, stream, n_part > 0, lg, n_part, p.T, p.E, p.k, p.router_mode,
+                        p.router_mult, p.router_bias, p.ids_out, p.wts_out);
     if (e != cudaSuccess) return e;
     RouteParams q = p;
-    q.logits = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
+    q.logits = nullptr; q.router_w = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
     return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, q);
   }
   return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, p);

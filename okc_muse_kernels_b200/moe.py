@@ -20,7 +20,7 @@ from . import _lib
 from ._lib import OkcError, Plan, Sizes
 
 __all__ = ["MoEPlan", "prepare", "kernel_fn", "moe_step", "route", "sorted_routes", "unpack_bf16", "read_status",
-           "experts_profiled", "experts_ep", "cast_bf16", "HostStep", "OkcError"]
+           "experts_profiled", "experts_ep", "cast_bf16", "HostStep", "route_hidden", "moe_layer_step", "OkcError"]
 
 
 @dataclass(frozen=True)
@@ -293,6 +293,51 @@ def route(router_logits: torch.Tensor, state: dict, *, own_tokens=None):
                                         state["ids"].data_ptr(), state["wts"].data_ptr(),
                                         state["workspace"].data_ptr(), _stream()), "okc_moe_route")
     return state["ids"][:T], state["wts"][:T]
+
+
+SIGMOID_MULTIPLIER = 0.1767766952966369   # the reference layer's ROUTER_MULTIPLIER (muse_decode_layer/reference.py:51)
+
+
+def route_hidden(hidden_states: torch.Tensor, router_w: torch.Tensor, state: dict, *, bias: torch.Tensor | None = None,
+                 mode: str = "softmax", multiplier: float = SIGMOID_MULTIPLIER, own_tokens=None):
+    """Router logits ``hidden . router_w^T`` (FP32, never materialised) + top-k + the token->expert sort.
+
+    ``mode="softmax"``: the softmax top-k of ``route``.  ``mode="sigmoid"``: the reference layer's router
+    (muse_decode_layer/reference.py:419-424): scores = sigmoid(multiplier * logits), ``bias`` f32 [E] is
+    added for the choice only, weights = chosen scores renormalised.  ``router_w`` f32 [E, H].
+    Returns views of the state's ``ids`` and ``wts`` buffers."""
+    plan: MoEPlan = state["plan"]
+    hidden, stride = _check_hidden(hidden_states, plan)
+    _need_cuda(router_w, bias)
+    if router_w.dtype != torch.float32 or tuple(router_w.shape) != (plan.n_experts, plan.hidden):
+        raise ValueError(f"router_w must be f32 [{plan.n_experts}, {plan.hidden}]")
+    if bias is not None and (bias.dtype != torch.float32 or tuple(bias.shape) != (plan.n_experts,)):
+        raise ValueError(f"bias must be f32 [{plan.n_experts}]")
+    if mode not in ("softmax", "sigmoid"):
+        raise ValueError("mode is 'softmax' or 'sigmoid'")
+    T = hidden.shape[0]
+    t0, t1 = _own(plan, T, own_tokens)
+    router_w = router_w.contiguous()
+    r = _lib.Router(w=router_w.data_ptr(), bias=None if bias is None else bias.contiguous().data_ptr(),
+                    mode=0 if mode == "softmax" else 1, multiplier=float(multiplier))
+    _lib.check(_lib.lib().okc_moe_route_hidden(C.byref(plan.c_plan()), C.byref(r), hidden.data_ptr(), stride, None, T,
+                                               t0, t1, state["ids"].data_ptr(), state["wts"].data_ptr(),
+                                               state["workspace"].data_ptr(), _stream()), "okc_moe_route_hidden")
+    return state["ids"][:T], state["wts"][:T]
+
+
+def moe_layer_step(hidden_states: torch.Tensor, router_w: torch.Tensor, state: dict, *, bias: torch.Tensor | None = None,
+                   mode: str = "softmax", multiplier: float = SIGMOID_MULTIPLIER, out_f32: bool = False,
+                   own_tokens=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``moe_step`` with the router matrix instead of precomputed logits: ``route_hidden`` then the experts."""
+    plan: MoEPlan = state["plan"]
+    hidden, stride = _check_hidden(hidden_states, plan)
+    T = hidden.shape[0]
+    route_hidden(hidden, router_w, state, bias=bias, mode=mode, multiplier=multiplier, own_tokens=own_tokens)
+    if out is None:
+        out = torch.empty((T, plan.hidden), dtype=torch.float32 if out_f32 else torch.bfloat16, device=hidden.device)
+    _experts(hidden, stride, T, state, out, out_f32)
+    return out
 
 
 def moe_step(hidden_states: torch.Tensor, router_logits: torch.Tensor, state: dict, *, out_f32: bool = False,

@@ -75,6 +75,66 @@ def route_sigmoid_topk(logits: np.ndarray, bias: np.ndarray, k: int, multiplier:
     return ids, w
 
 
+def router_scores(hidden_bf16: np.ndarray, router_w: np.ndarray, bias: np.ndarray | None = None,
+                  multiplier: float = 0.1767766952966369):
+    """The reference layer's router on the token rows (muse_decode_layer/reference.py:419-424): logits in
+    float64, (unbiased sigmoid scores, the biased scores that choose the top k), both float32 [T, E].
+    Also returns the float64 logits."""
+    h = bf16_to_f32(np.asarray(hidden_bf16)).astype(np.float64)
+    logits = h @ np.asarray(router_w, np.float64).T
+    scores = (1.0 / (1.0 + np.exp(-logits * multiplier))).astype(np.float32)
+    biased = scores if bias is None else (scores + np.asarray(bias, np.float32)).astype(np.float32)
+    return scores, biased, logits
+
+
+# tolerances of the reference's routing checker (muse_decode_layer/reference.py:68-76)
+ROUTE_TOL = 5e-2
+LOCAL_SLACK = (0.08, 4)
+DISTINCT_SLACK = (0.15, 2)
+KEEP_TOL = (0.03, 0.04)
+KEEP_TOKENS = 256
+
+
+def check_routing(ids: np.ndarray, biased: np.ndarray, k: int, local_start: int = 0, local_count: int | None = None):
+    """None if ``ids`` [T, k] are an acceptable top-k under the biased scores, else what is wrong:
+    the reference's tolerance-based checker (muse_decode_layer/reference.py:609-637), with the number
+    of experts, k and the local range as arguments instead of module constants."""
+    ids = np.asarray(ids, np.int64)
+    biased = np.asarray(biased, np.float32)
+    n_experts = biased.shape[1]
+    local_count = n_experts if local_count is None else local_count
+    if ids.min() < 0 or ids.max() >= n_experts:
+        return "expert id out of range"
+    ranked = np.sort(ids, axis=-1)
+    if (ranked[:, 1:] == ranked[:, :-1]).any():
+        return "a token routed to the same expert twice"
+    order = np.argsort(-biased, axis=-1, kind="stable")
+    best_idx = order[:, :k]
+    best_val = np.take_along_axis(biased, best_idx, axis=1)
+    gap = best_val[:, -1:] - np.take_along_axis(biased, ids, axis=1)
+    if gap.max() > ROUTE_TOL:
+        return f"an expert was chosen whose biased score is {float(gap.max()):.2e} below the k-th best"
+    ninth = np.take_along_axis(biased, order[:, k:k + 1], axis=1)
+    keep_tol = KEEP_TOL[0] if len(ids) <= KEEP_TOKENS else KEEP_TOL[1]
+    kept = (best_idx[:, :, None] == ids[:, None, :]).any(-1)
+    local = (best_idx - local_start) % n_experts < local_count
+    lost = local & ~kept & (best_val - ninth > keep_tol)
+    if lost.any():
+        return "a local expert well above the (k+1)-th best was dropped"
+
+    def load(x):
+        loc = x[(x - local_start) % n_experts < local_count]
+        return int(loc.size), int(np.unique(loc).size)
+
+    routes, distinct = load(ids)
+    ref_routes, ref_distinct = load(best_idx)
+    if routes < ref_routes * (1 - LOCAL_SLACK[0]) - LOCAL_SLACK[1]:
+        return f"{routes} local routes where the reference has {ref_routes}"
+    if distinct < ref_distinct * (1 - DISTINCT_SLACK[0]) - DISTINCT_SLACK[1]:
+        return f"{distinct} local experts touched where the reference touches {ref_distinct}"
+    return None
+
+
 def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int = 16):
     """Token -> expert sort of the local routes.
 

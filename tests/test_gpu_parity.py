@@ -289,6 +289,54 @@ def test_batch_sweep_rows_match_config2_single_rows(T):
     _check_out(out[sub], ref, f"batch {T}")
 
 
+def _near_tie_ok(ids_gpu, ids_ref, key, tol):
+    """Both id lists are in descending key order: where they differ, the r-th chosen keys are within tol."""
+    kg = np.take_along_axis(key, ids_gpu.astype(np.int64), axis=1)
+    kr = np.take_along_axis(key, ids_ref.astype(np.int64), axis=1)
+    return bool((np.abs(kg - kr)[ids_gpu != ids_ref] <= tol).all())
+
+
+@pytest.mark.parametrize("T,H,E,k,mode", [(32, 4096, 128, 8, "softmax"), (64, 7168, 256, 8, "sigmoid"), (5, 512, 16, 2, "sigmoid"),
+                                          (256, 1024, 160, 6, "softmax")])
+def test_route_from_hidden_states_matches_the_layer_router(T, H, E, k, mode):
+    """Router logits computed from the token rows on the GPU (FP32 split-K) + top-k, against the float64
+    logits of the oracle: the reference's tolerance checker passes, ids agree except at near ties, the
+    weights agree, and the sort tables are those of the chosen ids."""
+    dev = _dev()
+    g = torch.Generator(device="cpu").manual_seed(700 + T)
+    hidden = torch.randn((T, H), generator=g).to(torch.bfloat16)
+    router_w = (torch.randn((E, H), generator=g) * (1.0 / 64)).float()
+    bias = (torch.randn((E,), generator=g) * 0.05).float() if mode == "sigmoid" else None
+    plan = okc.MoEPlan(hidden=H, inter=256, n_experts=E, top_k=k, max_tokens=max(T, 16))
+    sz = plan.sizes()
+    state = {"plan": plan, "workspace": torch.zeros(sz.workspace_bytes, dtype=torch.uint8, device=dev),
+             "ids": torch.zeros((plan.max_tokens, k), dtype=torch.int32, device=dev),
+             "wts": torch.zeros((plan.max_tokens, k), dtype=torch.float32, device=dev)}
+    ids, wts = okc.route_hidden(hidden.to(dev), router_w.to(dev), state, bias=None if bias is None else bias.to(dev), mode=mode)
+    ids, wts = ids.cpu().numpy(), wts.cpu().numpy()
+    hb = hidden.view(torch.uint16).numpy()
+    scores, biased, logits = moe_np.router_scores(hb, router_w.numpy(), None if bias is None else bias.numpy())
+    if mode == "sigmoid":
+        assert moe_np.check_routing(ids, biased, k) is None
+        ref_ids, ref_w = moe_np.route_sigmoid_topk(logits.astype(np.float32), bias.numpy(), k)
+        key = biased
+        picked = np.take_along_axis(scores, ids.astype(np.int64), axis=1)
+        want_w = picked / (picked.sum(axis=1, keepdims=True) + 1e-15)
+    else:
+        ref_ids, ref_w = moe_np.route_softmax_topk(logits.astype(np.float32), k)
+        key = logits.astype(np.float32)
+        sel = np.take_along_axis(logits, ids.astype(np.int64), axis=1)
+        ex = np.exp(sel - sel.max(axis=1, keepdims=True))
+        want_w = ex / ex.sum(axis=1, keepdims=True)
+    assert _near_tie_ok(ids, ref_ids, key, 2e-5 * max(1.0, float(np.abs(key).max())))
+    assert (ids == ref_ids).all(axis=1).mean() > 0.9
+    assert np.allclose(wts, want_w, rtol=2e-4, atol=1e-6)
+    s = okc.sorted_routes(state, T)
+    ref = moe_np.sort_routes(ids, 0, E, chunk=16 if (T <= 64 or T * k <= 8 * E) else 32)
+    assert np.array_equal(s["counts"][:E].cpu().numpy(), ref["counts"])
+    assert np.array_equal(s["pos"].cpu().numpy(), ref["pos"])
+
+
 def test_experts_run_again_on_the_same_routes():
     """The GEMM launch leaves its counters at zero, so the expert phase can be repeated without a new
     route call (three times here), with bit-identical results."""

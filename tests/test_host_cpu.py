@@ -192,3 +192,22 @@ def test_layout_pack_folds_zero_and_negative_scales_into_codes():
     assert np.array_equal(vals, want)
     scales = img[layout.TILE_CODE_BYTES:].reshape(layout.CHUNKS, layout.TILE_ROWS, 2)
     assert scales[0, 1, 1] == layout.SCALE_CODE[0x38]
+
+
+def test_oracle_layer_router_and_routing_checker():
+    """router_scores + route_sigmoid_topk pass the restated checker; a perturbed choice fails it."""
+    rng = np.random.default_rng(5)
+    T, H, E, k = 12, 256, 64, 8
+    hidden = moe_np.f32_to_bf16(rng.standard_normal((T, H)).astype(np.float32))
+    w = (rng.standard_normal((E, H)) / 16).astype(np.float32)
+    bias = (rng.standard_normal(E) * 0.05).astype(np.float32)
+    scores, biased, logits = moe_np.router_scores(hidden, w, bias)
+    ids, wts = moe_np.route_sigmoid_topk(logits.astype(np.float32), bias, k)
+    assert moe_np.check_routing(ids, biased, k) is None
+    assert np.allclose(wts.sum(axis=1), 1.0, atol=1e-6)
+    bad = ids.copy()
+    bad[0, 0] = int(np.argmin(biased[0]))            # the worst expert instead of the best
+    assert moe_np.check_routing(bad, biased, k) is not None
+    dup = ids.copy()
+    dup[1, 1] = dup[1, 0]
+    assert "twice" in moe_np.check_routing(dup, biased, k)
