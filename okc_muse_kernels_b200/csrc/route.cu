@@ -31,51 +31,77 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { retur
 // hidden[t][k] * w[e][k], FP32 multiply-adds in ascending k (bf16 -> f32 is exact).  The step before
 // the MoE path in the reference's layer (muse_decode_layer/layer.py:325-351, _router_split), fused
 // here with the routing: the logits never exist as a tensor, the top-k kernel adds the splits (in
-// split order) as it loads them.  grid (E / 16, splits), 256 threads: thread = (expert e0 + tid % 16,
-// tokens tid / 16 + 16 j).
+// split order) as it loads them.  grid (E / 16, splits), 256 threads.
 constexpr int kRtE = 16, kRtK = 64, kRtMaxT = 256;
+// JT = token groups of 32 the step has (T <= 32 JT): loops over tokens stop there.
+template <int JT>
 __global__ void __launch_bounds__(256) okc_router_partial(const uint16_t* __restrict__ hidden, int64_t stride,
                                                           const float* __restrict__ w, int T, int H, int E, int kc,
                                                           float* __restrict__ part) {
   __shared__ uint32_t hs[kRtMaxT][kRtK / 2 + 1];   // bf16 pairs, rows padded against bank conflicts
-  __shared__ float ws[kRtE][kRtK + 1];
-  const int tid = threadIdx.x, e = tid & 15, tg = tid >> 4;
+  __shared__ __align__(16) float ws[kRtE][kRtK + 2]; // even row stride: a thread reads k pairs as 8 bytes
+  // thread = experts e0 + 2 eg, + 1 and tokens tg + 32 j
+  const int tid = threadIdx.x, eg = tid & 7, tg = tid >> 3;
   const int e0 = blockIdx.x * kRtE;
   const int k_begin = blockIdx.y * kc, k_end = min(H, k_begin + kc);
-  float acc[kRtMaxT / 16];
+  const int n_vec = T * (kRtK / 8);                // 16-byte vectors of the token rows per chunk
+  float acc[2][JT];
 #pragma unroll
-  for (int j = 0; j < kRtMaxT / 16; ++j) acc[j] = 0.f;
+  for (int j = 0; j < JT; ++j) acc[0][j] = acc[1][j] = 0.f;
+
+  // the next chunk travels from global memory into registers while the current one is multiplied
+  uint4 hreg[JT];       // 32 JT tokens x 8 vectors / 256 threads
+  float4 wreg = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int q = 0; q < JT; ++q) {
+      const int i = tid + 256 * q;
+      if (i < n_vec) {
+        const int t = i >> 3, v = i & 7;
+        hreg[q] = *reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * stride + k0 + v * 8);
+      }
+    }
+    wreg = *reinterpret_cast<const float4*>(w + static_cast<size_t>(e0 + (tid >> 4)) * H + k0 + (tid & 15) * 4);
+  };
+  if (k_begin < k_end) fetch(k_begin);
   for (int k0 = k_begin; k0 < k_end; k0 += kRtK) {
-    __syncthreads();
-    for (int i = tid; i < T * (kRtK / 8); i += 256) {          // 16-byte vectors of the token rows
-      const int t = i / (kRtK / 8), v = i - t * (kRtK / 8);
-      const uint4 x = *reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * stride + k0 + v * 8);
-      hs[t][v * 4 + 0] = x.x; hs[t][v * 4 + 1] = x.y; hs[t][v * 4 + 2] = x.z; hs[t][v * 4 + 3] = x.w;
+    __syncthreads();                               // the previous chunk has been consumed
+#pragma unroll
+    for (int q = 0; q < JT; ++q) {
+      const int i = tid + 256 * q;
+      if (i < n_vec) {
+        const int t = i >> 3, v = i & 7;
+        hs[t][v * 4 + 0] = hreg[q].x; hs[t][v * 4 + 1] = hreg[q].y; hs[t][v * 4 + 2] = hreg[q].z; hs[t][v * 4 + 3] = hreg[q].w;
+      }
     }
     {
-      const int r = tid >> 4, v = tid & 15;                       // 16 rows x 16 float4
-      const float4 x = *reinterpret_cast<const float4*>(w + static_cast<size_t>(e0 + r) * H + k0 + v * 4);
-      ws[r][v * 4 + 0] = x.x; ws[r][v * 4 + 1] = x.y; ws[r][v * 4 + 2] = x.z; ws[r][v * 4 + 3] = x.w;
+      const int r = tid >> 4, v = tid & 15;
+      ws[r][v * 4 + 0] = wreg.x; ws[r][v * 4 + 1] = wreg.y; ws[r][v * 4 + 2] = wreg.z; ws[r][v * 4 + 3] = wreg.w;
     }
     __syncthreads();
+    if (k0 + kRtK < k_end) fetch(k0 + kRtK);
 #pragma unroll 4
     for (int k2 = 0; k2 < kRtK / 2; ++k2) {
-      const float w0 = ws[e][2 * k2], w1 = ws[e][2 * k2 + 1];
+      const float2 wa = *reinterpret_cast<const float2*>(&ws[2 * eg][2 * k2]);
+      const float2 wb = *reinterpret_cast<const float2*>(&ws[2 * eg + 1][2 * k2]);
 #pragma unroll
-      for (int j = 0; j < kRtMaxT / 16; ++j) {
-        const int t = tg + 16 * j;
+      for (int j = 0; j < JT; ++j) {
+        const int t = tg + 32 * j;
         if (t < T) {
           const uint32_t hv = hs[t][k2];
-          acc[j] = fmaf(__uint_as_float(hv << 16), w0, acc[j]);
-          acc[j] = fmaf(__uint_as_float(hv & 0xFFFF0000u), w1, acc[j]);
+          const float h0 = __uint_as_float(hv << 16), h1 = __uint_as_float(hv & 0xFFFF0000u);
+          acc[0][j] = fmaf(h1, wa.y, fmaf(h0, wa.x, acc[0][j]));
+          acc[1][j] = fmaf(h1, wb.y, fmaf(h0, wb.x, acc[1][j]));
         }
       }
     }
   }
 #pragma unroll
-  for (int j = 0; j < kRtMaxT / 16; ++j) {
-    const int t = tg + 16 * j;
-    if (t < T) part[(static_cast<size_t>(blockIdx.y) * T + t) * E + e0 + e] = acc[j];
+  for (int j = 0; j < JT; ++j) {
+    const int t = tg + 32 * j;
+    if (t < T)
+      *reinterpret_cast<float2*>(part + (static_cast<size_t>(blockIdx.y) * T + t) * E + e0 + 2 * eg) =
+          make_float2(acc[0][j], acc[1][j]);
   }
 }
 
@@ -396,8 +422,11 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
       // logits = hidden . router_w^T as split-K partial sums in scratch; the top-k kernel adds the splits
       n_part = p.router_splits;
       const int kc = ((p.H / kRtK + n_part - 1) / n_part) * kRtK;
-      okc_router_partial<<<dim3(p.E / kRtE, n_part), 256, 0, stream>>>(p.hidden, p.hidden_stride, p.router_w, p.T, p.H, p.E,
-                                                                      kc, p.router_part);
+      const dim3 rgrid(p.E / kRtE, n_part);
+      if (p.T <= 32) okc_router_partial<1><<<rgrid, 256, 0, stream>>>(p.hidden, p.hidden_stride, p.router_w, p.T, p.H, p.E, kc, p.router_part);
+      else if (p.T <= 64) okc_router_partial<2><<<rgrid, 256, 0, stream>>>(p.hidden, p.hidden_stride, p.router_w, p.T, p.H, p.E, kc, p.router_part);
+      else if (p.T <= 128) okc_router_partial<4><<<rgrid, 256, 0, stream>>>(p.hidden, p.hidden_stride, p.router_w, p.T, p.H, p.E, kc, p.router_part);
+      else okc_router_partial<8><<<rgrid, 256, 0, stream>>>(p.hidden, p.hidden_stride, p.router_w, p.T, p.H, p.E, kc, p.router_part);
       e = cudaGetLastError();
       if (e != cudaSuccess) return e;
       lg = p.router_part;
