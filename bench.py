@@ -32,7 +32,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 # dram bytes of one okc_moe_gemm launch under ncu, configuration 2 with 115 touched experts
-NCU_TRAFFIC_C2_115 = 820.4e6 + 413.3e6
+NCU_TRAFFIC_C2_115 = 1223.3e6 + 6.7e6
 SEEDS = (7, 8, 9)
 METRIC = "moe_step_weight_stream_bandwidth"
 UNIT = "GB/s"
