@@ -511,6 +511,11 @@ def run_gpu(args):
                "seconds_per_step": full_s,
                "sample": f"{len(sample)} of {touched[0]} touched experts of one step (torch CPU dequantise + 2 FP32 matmuls each), scaled to the step"}
 
+    # kernels of this library per step beyond the single-GPU step's: the token push and, unless the
+    # combine is fused with the reduce-scatter, the pull-reduce (peer exchange); the cast (NCCL exchange)
+    ep_extra_launches = 0
+    if world > 1:
+        ep_extra_launches = (1 if layer.fuse_combine else 2) if layer.exchange == "peer" else 1
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_per_step, "us_per_step": 1e3 * ms_per_step, "higher_is_better": True,
@@ -521,7 +526,7 @@ def run_gpu(args):
                            "router": "logits = hidden . router_w^T computed inside the step" if router_w is not None else "logits given",
                            "touched_experts_per_seed": touched, "routing_seeds": list(SEEDS)},
                 "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-                "gpu_launches": (_lib.lib().okc_moe_launches_per_step() + (0 if world == 1 else 2 if layer.exchange == "peer" else 1)) * args.steps,
+                "gpu_launches": (_lib.lib().okc_moe_launches_per_step() + ep_extra_launches) * args.steps,
                 "step_ms_median": statistics.median(times_ms), "step_ms_min": min(times_ms)}
         print(json.dumps(line), flush=True)
     if world > 1:
