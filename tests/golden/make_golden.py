@@ -113,7 +113,9 @@ def router_vectors(starter_route) -> dict:
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of tech-cosmos/okc-muse-kernels>")
+    root = sys.argv[1]
     sys.path.insert(0, os.path.join(root, "muse_moe_w4a16"))
     nvfp4 = importlib.import_module("nvfp4")
     ref = importlib.import_module("reference")
