@@ -1,10 +1,14 @@
 """Benchmark of the NVFP4 W4A16 MoE decode step.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c1|c4|c5] [--tokens T]
+    python bench.py --sweep            # configuration 3: one line per batch size T = 1 ... 256
 
-N = 1: configuration 2 (T=32, H=4096, I=1536, E=128, top-8, all experts on the GPU).
+N = 1: configuration 2 (T=32, H=4096, I=1536, E=128, top-8, all experts on the GPU); the line also
+carries `c4_n1`, configuration 4 on this one GPU, as the anchor of the 1 -> 8 GPU curve.
 N > 1 (launched by torch.distributed.run, one rank per GPU): configuration 4 (T=128, H=7168, I=2048,
 E=256 sharded contiguously + a replicated shared expert), all-gather -> local experts -> reduce-scatter.
+Every run compares the output of one step with the CPU oracle on a token subset (`parity`) and exits
+non-zero when that fails.
 
 A step is one MoE layer call on one batch of seeded synthetic inputs (three routing seeds, rotated).
 `value` is the weight-stream rate: the algorithmic bytes of the step (FP4 codes + E4M3 scales of every
@@ -31,8 +35,6 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# dram bytes of one okc_moe_gemm launch under ncu, configuration 2 with 115 touched experts
-NCU_TRAFFIC_C2_115 = 1223.3e6 + 6.7e6
 SEEDS = (7, 8, 9)
 METRIC = "moe_step_weight_stream_bandwidth"
 UNIT = "GB/s"
@@ -168,64 +170,6 @@ def _touched(ids: np.ndarray, lo: int, cnt: int) -> int:
     return int(((u >= lo) & (u < lo + cnt)).sum())
 
 
-# --------------------------------------------------------------------------------------- CPU arm
-def run_reference_arm(args):
-    """`--impl reference`: the reference's CPU path (its eager dequantise-then-matmul, restated in
-    oracle/) on the host cores.  Each step times a bounded sample of the step's touched experts and
-    scales the time to all of them; rank 0 alone works."""
-    if int(os.environ.get("RANK", "0")) != 0:
-        return
-    import torch
-    from okc_muse_kernels_b200 import synth
-    from oracle import moe_torch
-    wl = synth.WORKLOADS[args.workload or ("c2" if args.gpus == 1 else "c4")]
-    tokens = args.tokens or wl.tokens
-    n_sample = 4
-    torch.set_num_threads(os.cpu_count() or 1)
-    keys = ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs")
-    cache: dict = {}
-    per_step, step_bytes = [], []
-    for i in range(args.warmup + args.steps):
-        hidden, logits = synth.make_inputs(wl, seed=SEEDS[i % len(SEEDS)], device="cpu", tokens=tokens)
-        ids, w = moe_torch.route_softmax_topk(logits, wl.top_k)
-        touched = sorted(int(e) for e in torch.unique(ids).tolist())
-        sample = touched[:n_sample]
-        for e in sample:      # only the sampled experts' weights are generated
-            if e not in cache:
-                cache[e] = synth.make_weights(wl, device="cpu", n_experts=1, first_expert=e)
-        wn = {k: _IndexByExpert({e: cache[e][k][0] for e in sample}, wl.n_experts) for k in keys}
-        t0 = time.perf_counter()
-        moe_torch.experts(hidden, ids, w, wn, only_experts=set(sample))
-        dt = time.perf_counter() - t0
-        if i >= args.warmup:
-            per_step.append(dt * len(touched) / len(sample))
-            step_bytes.append(synth.algorithmic_bytes(wl, len(touched), tokens, shared=False))
-    ms = 1e3 * statistics.mean(per_step)
-    gbs = statistics.mean(step_bytes) / (ms * 1e-3) / 1e9
-    sample_desc = (f"{n_sample} of the step's touched experts per step (dequantise + 2 FP32 matmuls each, torch CPU ops), "
-                   "time scaled to all touched experts")
-    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "us_per_step": 1e3 * ms, "higher_is_better": True,
-            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": _workload_name(wl, tokens, args.gpus)},
-            "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": sample_desc},
-            "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
-
-
-class _IndexByExpert:
-    """weights[key][e] for a sparse set of experts, with the leading dimension the oracle asks for."""
-
-    def __init__(self, by_expert: dict, n_experts: int):
-        self.by_expert = by_expert
-        first = next(iter(by_expert.values()))
-        self.shape = (n_experts,) + tuple(np.shape(first))
-
-    def __getitem__(self, e):
-        return self.by_expert[int(e)]
-
-
 def _workload_name(wl, tokens, gpus):
     s = (f"{wl.name}: T={tokens} H={wl.hidden} I={wl.inter} E={wl.n_experts} top-{wl.top_k} NVFP4 W4A16 MoE decode step"
          + (f" + shared expert I={wl.shared_inter}" if wl.shared_inter else ""))
@@ -234,53 +178,175 @@ def _workload_name(wl, tokens, gpus):
     return s
 
 
+def _config(wl, tokens, gpus):
+    """The same dictionary in both arms (the driver compares them)."""
+    return {"workload": _workload_name(wl, tokens, gpus),
+            "l2": "a 256 MB buffer is read between timed steps (cold L2); the touched weights of a step also exceed the "
+                  "126 MB L2 in every configuration but c1",
+            "routing_seeds": list(SEEDS)}
+
+
+class _IndexByExpert:
+    """weights[key][e] for a sparse set of experts, with the leading dimension the oracle asks for."""
+
+    def __init__(self, by_expert: dict, key: str, n_experts: int):
+        self.by_expert, self.key = by_expert, key
+        first = next(iter(by_expert.values()))[key]
+        self.shape = (n_experts,) + tuple(first.shape)
+
+    def __getitem__(self, e):
+        return self.by_expert[int(e)][self.key]
+
+
+_KEYS = ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs")
+
+
+def _cpu_expert(wl, e, device):
+    """One expert's NVFP4 tensors on the CPU (generated on `device` from the expert's own seed)."""
+    from okc_muse_kernels_b200 import synth
+    one = synth.make_weights(wl, device=device, n_experts=1, first_expert=int(e))
+    return {k: one[k][0].cpu() for k in _KEYS}
+
+
+def _cpu_shared(wl, device):
+    from okc_muse_kernels_b200 import synth
+    one = synth.make_weights(wl, device=device, n_experts=0)
+    return {k[len("shared_"):]: v.cpu() for k, v in one.items() if k.startswith("shared_")}
+
+
+# --------------------------------------------------------------------------------------- CPU arm
+def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU path (its eager dequantise-then-matmul, restated in
+    oracle/moe_torch.py with the torch operators the reference uses) on all host cores, on this arm's
+    workload.  A step times every touched expert of the step when the run's time budget allows
+    (`sampled_fraction` 1.0: configuration 2); otherwise as many whole experts as fit, the time scaled
+    to all touched experts and `sampled_fraction` says how much was timed.  Rank 0 alone works."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+    from okc_muse_kernels_b200 import synth
+    from oracle import moe_torch
+    wl = synth.WORKLOADS[args.workload or ("c2" if args.gpus == 1 else "c4")]
+    tokens = args.tokens or wl.tokens
+    torch.set_num_threads(os.cpu_count() or 1)
+    budget_s = float(os.environ.get("OKC_REF_BUDGET_S", "150"))
+    n_steps = args.warmup + args.steps
+    cache: dict = {}
+
+    def expert(e):
+        if e not in cache:
+            cache[e] = _cpu_expert(wl, e, "cpu")
+        return cache[e]
+
+    shared = _cpu_shared(wl, "cpu") if wl.shared_inter else None
+    # calibration: one expert, twice (the first call warms the thread pool up)
+    hidden, logits = synth.make_inputs(wl, seed=SEEDS[0], device="cpu", tokens=tokens)
+    ids, w = moe_torch.route_softmax_topk(logits, wl.top_k)
+    e0 = int(ids[0, 0])
+    wn = {k: _IndexByExpert({e0: expert(e0)}, k, wl.n_experts) for k in _KEYS}
+    moe_torch.experts(hidden, ids, w, wn, only_experts={e0})
+    c0 = time.perf_counter()
+    moe_torch.experts(hidden, ids, w, wn, only_experts={e0})
+    t_expert = time.perf_counter() - c0
+    per_step = max(1, int(budget_s / max(n_steps, 1) / max(t_expert, 1e-6)))
+
+    per_step_s, step_bytes, fractions, wall = [], [], [], 0.0
+    for i in range(n_steps):
+        hidden, logits = synth.make_inputs(wl, seed=SEEDS[i % len(SEEDS)], device="cpu", tokens=tokens)
+        ids, w = moe_torch.route_softmax_topk(logits, wl.top_k)
+        touched = sorted(int(e) for e in torch.unique(ids).tolist())
+        units = len(touched) + (1 if shared is not None else 0)
+        sample = touched[:per_step]
+        with_shared = shared is not None and len(sample) == len(touched)
+        by = {e: expert(e) for e in sample}                     # generated outside the timed region
+        wn = {k: _IndexByExpert(by, k, wl.n_experts) for k in _KEYS}
+        t0 = time.perf_counter()
+        acc = moe_torch.experts(hidden, ids, w, wn, only_experts=set(sample))
+        if with_shared:
+            acc = acc + moe_torch.shared_expert(hidden, shared)
+        acc.to(torch.bfloat16)
+        dt = time.perf_counter() - t0
+        timed = len(sample) + (1 if with_shared else 0)
+        if i >= args.warmup:
+            wall += dt
+            per_step_s.append(dt * units / timed)
+            fractions.append(timed / units)
+            step_bytes.append(synth.algorithmic_bytes(wl, len(touched), tokens, shared=shared is not None))
+    ms = 1e3 * statistics.mean(per_step_s)
+    gbs = statistics.mean(step_bytes) / (ms * 1e-3) / 1e9
+    frac = statistics.mean(fractions)
+    sample_desc = ("every touched expert of every step (dequantise + 2 FP32 matmuls each, torch CPU operators)" if frac == 1.0 else
+                   f"{per_step} of the step's touched experts per step (dequantise + 2 FP32 matmuls each, torch CPU operators), "
+                   "time scaled to all touched experts")
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms if frac == 1.0 else 1e3 * wall / args.steps,
+            "ms_per_step_whole_workload": ms, "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": _config(wl, tokens, args.gpus), "sampled_fraction": frac,
+            "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": sample_desc},
+            "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
 # --------------------------------------------------------------------------------------- GPU arm
-def run_gpu(args):
+def _parity(wl, hidden, logits, out_rows, row0, ids_gpu, dev, n_tokens):
+    """Output rows [row0, row0 + len(out_rows)) of one step against the CPU oracle (the torch statement
+    of the reference's eager path) on a token subset, and the routing ids of every token against the
+    oracle's stable top-k.  Tolerances of this path: ids bit-exact, max-abs <= 2e-2, rel-L2 <= 1e-2."""
+    import torch
+    from oracle import moe_np, moe_torch
+    ids_ref, wts_ref = moe_np.route_softmax_topk(logits.cpu().numpy(), wl.top_k)
+    ids_exact = bool(np.array_equal(ids_gpu.cpu().numpy(), ids_ref))
+    n = out_rows.shape[0]
+    pick = sorted({0, n - 1, n // 2, n // 3})[:n_tokens]
+    sub = [row0 + i for i in pick]
+    by = {int(e): _cpu_expert(wl, e, dev) for e in np.unique(ids_ref[sub])}
+    wn = {k: _IndexByExpert(by, k, wl.n_experts) for k in _KEYS}
+    h_sub = hidden.cpu()[sub]
+    ref = moe_torch.experts(h_sub, torch.from_numpy(ids_ref[sub]).long(), torch.from_numpy(wts_ref[sub]), wn)
+    if wl.shared_inter:
+        ref = ref + moe_torch.shared_expert(h_sub, _cpu_shared(wl, dev))
+    ref = ref.double().numpy()
+    got = out_rows[pick].float().cpu().double().numpy()
+    max_abs = float(np.abs(got - ref).max())
+    rel = float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-12))
+    ok = ids_exact and bool(np.isfinite(got).all()) and max_abs <= 2e-2 and rel <= 1e-2
+    return {"ok": ok, "ids_exact": ids_exact, "max_abs": max_abs, "rel_l2": rel, "tokens": len(sub)}
+
+
+def measure(wl, tokens, args, dev, world, rank, *, state=None, layer=None, with_e2e=True, with_parity=True,
+            with_clocks=True, steps=None, max_tokens=None):
+    """Builds the workload on this rank (unless `state` is given), times `steps` steps and returns the
+    figures of the JSON line as a dictionary (on every rank)."""
     import torch
     import torch.distributed as dist
 
     import okc_muse_kernels_b200 as okc
-    from okc_muse_kernels_b200 import _lib, ep, synth
+    from okc_muse_kernels_b200 import ep, synth
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    wl = synth.WORKLOADS[args.workload or ("c2" if world == 1 else "c4")]
-    tokens = args.tokens or wl.tokens
+    steps = steps or args.steps
     peak_gbs, peak_kind = _peaks()
-
-    # ---- state
-    if world == 1:
-        plan = okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=wl.n_experts, top_k=wl.top_k,
-                           shared_inter=wl.shared_inter, max_tokens=max(tokens, 16))
-        weights = synth.make_weights(wl, device=dev)
-        state = okc.prepare(weights, plan)
-        layer = None
-    else:
-        plan = ep.shard_plan(wl.hidden, wl.inter, wl.n_experts, wl.top_k, world, rank, max_tokens=max(tokens, 16),
-                             shared_inter=wl.shared_inter)
-        weights = synth.make_weights(wl, device=dev, n_experts=plan.local_count, first_expert=plan.local_start)
-        # the exchange steps over peer memory with this library's kernels; NCCL collectives if the
-        # ranks' buffers cannot be mapped into each other (every rank takes the same branch)
-        layer = None
-        if args.exchange == "peer":
-            try:
-                layer = ep.ExpertParallelMoE(plan, tokens, weights=weights, exchange="peer")
-            except Exception as exc:      # noqa: BLE001
-                print(f"rank {rank}: peer-memory exchange unavailable ({exc}); using NCCL collectives", file=sys.stderr)
-        if layer is None:
-            layer = ep.ExpertParallelMoE(plan, tokens, weights=weights, exchange="nccl")
-        state = layer.state
-    del weights
-    torch.cuda.empty_cache()
+    local_rank = dev.index
+    max_tokens = max(max_tokens or tokens, 16)
+    if state is None:
+        if world == 1:
+            plan = okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=wl.n_experts, top_k=wl.top_k,
+                               shared_inter=wl.shared_inter, max_tokens=max_tokens)
+            weights = synth.make_weights(wl, device=dev)
+            state = okc.prepare(weights, plan)
+        else:
+            plan = ep.shard_plan(wl.hidden, wl.inter, wl.n_experts, wl.top_k, world, rank, max_tokens=max_tokens,
+                                 shared_inter=wl.shared_inter)
+            weights = synth.make_weights(wl, device=dev, n_experts=plan.local_count, first_expert=plan.local_start)
+            # --exchange peer: this library's kernels over peer memory.  If the ranks' buffers cannot be mapped
+            # into each other the constructor raises on every rank and the run fails: a scaling record must
+            # not change its data path silently.
+            layer = ep.ExpertParallelMoE(plan, tokens, weights=weights, exchange=args.exchange)
+            state = layer.state
+        del weights
+        torch.cuda.empty_cache()
+    plan = state["plan"]
 
     inputs = [synth.make_inputs(wl, seed=s, device=dev, tokens=tokens) for s in SEEDS]
     t0, t1 = ep.token_block(tokens, world, rank) if world > 1 else (0, tokens)
@@ -293,7 +359,6 @@ def run_gpu(args):
         flush_sink.add_(flush.view(torch.int64)[::64].sum())
 
     # --route-from-hidden (N = 1): the router logits are computed from the token rows inside the step
-    # (okc.moe_layer_step: hidden . router_w^T in FP32, then softmax top-k) instead of being an input
     router_w = None
     if args.route_from_hidden:
         if world > 1:
@@ -311,9 +376,11 @@ def run_gpu(args):
             return okc.route_hidden(h, router_w, state)
         return okc.route(lg, state, own_tokens=(t0, t1))
 
-    # ---- the step: graph replay at N = 1, eager collectives + kernels at N > 1
+    # ---- the step as a CUDA graph per routing seed
     outs = [torch.empty((tokens, wl.hidden), dtype=torch.bfloat16, device=dev) for _ in SEEDS]
     graphs = []
+    exch = "" if world == 1 else ("peer-memory exchange kernels" if layer.exchange == "peer" else "NCCL collectives")
+    timing = "CUDA-graph replay per step"
     if world == 1:
         for (h, lg), o in zip(inputs, outs):
             one_step(h, lg, o)                     # eager warm-up (sets kernel attributes)
@@ -323,36 +390,21 @@ def run_gpu(args):
             with torch.cuda.graph(g):
                 one_step(h, lg, o)
             graphs.append(g)
-
-    exch = "" if world == 1 else ("peer-memory exchange kernels" if layer.exchange == "peer" else "NCCL collectives")
-    ep_timing = f"eager launches + {exch} per step"
-    if world > 1:
-        # the expert-parallel step (two all-gathers, five kernels, a reduce-scatter, a cast) as one CUDA
-        # graph per routing seed: at 8 ranks a rank's kernels take about as long as the host needs to
-        # launch them one by one.  Every rank captures; if capture is refused the step stays eager.
+    else:
         own = [(h[t0:t1].contiguous(), lg[t0:t1].contiguous()) for h, lg in inputs]
         for ho, lo in own:
             layer.step(ho, lo)
         torch.cuda.synchronize()
         dist.barrier()
-        try:
-            if not args.ep_graphs:
-                raise RuntimeError("not requested")
+        if args.ep_graphs:
             for ho, lo in own:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     layer.step(ho, lo)
                 graphs.append(g)
-            ep_timing = f"CUDA-graph replay per step (kernels + {exch} captured)"
-        except Exception as exc:      # noqa: BLE001 - any capture failure means: run eagerly
-            graphs = []
-            if args.ep_graphs:
-                print(f"rank {rank}: graph capture of the expert-parallel step failed ({exc}); running eagerly", file=sys.stderr)
-        ok_flag = torch.tensor([1 if graphs else 0], device=dev)
-        dist.all_reduce(ok_flag, op=dist.ReduceOp.MIN)
-        if int(ok_flag.item()) == 0:
-            graphs = []
-            ep_timing = f"eager launches + {exch} per step"
+            timing = f"CUDA-graph replay per step (kernels + {exch} captured)"
+        else:
+            timing = f"eager launches + {exch} per step"
 
     def step(i):
         j = i % len(SEEDS)
@@ -367,17 +419,14 @@ def run_gpu(args):
     for h, lg in inputs:
         ids, _ = do_route(h, lg)
         touched.append(_touched(ids.cpu().numpy(), plan.local_start, plan.local_count))
-    bytes_per_seed = [synth.algorithmic_bytes(wl, n, tokens if world == 1 else tokens, shared=bool(wl.shared_inter))
-                      for n in touched]
+    bytes_per_seed = [synth.algorithmic_bytes(wl, n, tokens, shared=bool(wl.shared_inter)) for n in touched]
 
     # ---- roofline of the dominant kernel (the grouped-GEMM launch): CUDA events around each kernel of the
-    # expert phase, taken before the timed region (right after a long back-to-back run the same kernels
-    # were measured up to 5 % slower between their events than they run inside the replayed step)
+    # expert phase, taken before the timed region
     phases = {"gather": [], "gemm": [], "combine": [], "total": []}
     prof_out = torch.empty((tokens, wl.hidden), dtype=torch.float32 if world > 1 else torch.bfloat16, device=dev)
-    n_prof = 15
-    gate_up_bytes = []
-    for i in range(n_prof + 2):
+    gemm_bytes = []
+    for i in range(15 + 2):
         j = i % len(SEEDS)
         h, lg = inputs[j]
         do_route(h, lg)
@@ -389,23 +438,20 @@ def run_gpu(args):
                 phases[k].append(ms[k])
             n_exp = touched[j] + (1 if wl.shared_inter else 0)
             # weight stream of both GEMMs (4 bits + 1/16 scale byte per element) + the gathered token rows
-            gate_up_bytes.append(n_exp * 3 * wl.inter * wl.hidden * 9 // 16 + tokens * wl.top_k * wl.hidden * 2)
+            gemm_bytes.append(n_exp * 3 * wl.inter * wl.hidden * 9 // 16 + tokens * wl.top_k * wl.hidden * 2)
 
-    # the clock sampler starts before the warm-up; samples from before the timed region are dropped
-    # when NVML is read in-process (the nvidia-smi fallback keeps them: it is slow to start, and they
-    # too were taken under this workload)
-    sampler = NvmlSampler(local_rank)
-    if rank == 0:
+    sampler = NvmlSampler(local_rank) if (with_clocks and rank == 0) else None
+    if sampler is not None:
         sampler.start()
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    if rank == 0 and sampler.fallback is None:
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    if sampler is not None and sampler.fallback is None:
         sampler.mark()
-    for i in range(args.steps):
+    for i in range(steps):
         flush_l2()
         ev[i][0].record()
         step(i)
@@ -413,47 +459,46 @@ def run_gpu(args):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if sampler is not None else None
     times_ms = [a.elapsed_time(b) for a, b in ev]
-    total_ms = sum(times_ms)
-    step_bytes = sum(bytes_per_seed[i % len(SEEDS)] for i in range(args.steps))
+    my_ms = sum(times_ms)
+    my_bytes = sum(bytes_per_seed[i % len(SEEDS)] for i in range(steps))
     rc, detail = okc.read_status(state)
     if rc != 0:
-        raise SystemExit(f"device status {rc} detail {detail:#x}")
+        raise SystemExit(f"rank {rank}: device status {rc} detail {detail:#x}")
     if world > 1 and layer.peer is not None:
         rc, detail = layer.peer.read_status()
         if rc != 0:
             raise SystemExit(f"rank {rank}: exchange status {rc} detail {detail:#x}")
 
+    total_ms, step_bytes, per_rank = my_ms, float(my_bytes), None
     if world > 1:
-        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        t = torch.tensor([my_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
-        b = torch.tensor([float(step_bytes)], dtype=torch.float64, device=dev)
+        b = torch.tensor([float(my_bytes)], dtype=torch.float64, device=dev)
         dist.all_reduce(b, op=dist.ReduceOp.SUM)
         step_bytes = float(b.item())
-    ms_per_step = total_ms / args.steps
+        mine = {"rank": rank, "touched_experts": touched, "bytes_per_step": my_bytes / steps, "step_ms": my_ms / steps,
+                "gemm_ms": statistics.median(phases["gemm"])}
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, mine)
+    ms_per_step = total_ms / steps
     value = step_bytes / (total_ms * 1e-3) / 1e9
 
-    # ---- roofline figures from the per-kernel events taken before the timed region
-    roof = None
-    gu_ms = statistics.median(phases["gemm"])
-    achieved = statistics.mean(gate_up_bytes) / (gu_ms * 1e-3) / 1e9
-    # DRAM traffic of one launch from the ncu capture summarised under profiles/
-    # (dram__bytes_read.sum + dram__bytes_write.sum at 115 touched experts of configuration 2),
-    # scaled to this run's touched experts: the traffic is the weight stream, which grows in proportion
-    traffic = None
-    if wl.name == "c2":
-        traffic = NCU_TRAFFIC_C2_115 / 115.0 * statistics.mean(touched)
-    roof = {"kernel": "okc_moe_gemm (gate_up + SiLU*mul units, then down units, one launch)", "bound": "hbm", "achieved": achieved, "peak": peak_gbs,
-            "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": traffic,
+    gemm_ms = statistics.median(phases["gemm"])
+    achieved = statistics.mean(gemm_bytes) / (gemm_ms * 1e-3) / 1e9
+    roof = {"kernel": "okc_moe_gemm (gate_up + SiLU*mul units, then down units, one launch)", "bound": "hbm",
+            "achieved": achieved, "peak": peak_gbs, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+            "frac": achieved / peak_gbs, "traffic": None,
+            "traffic_source": "not captured in this run; the ncu capture of this kernel (dram__bytes_read.sum + "
+                              "dram__bytes_write.sum against the algorithmic bytes) is summarised in profiles/moe_gemm_c2.md",
             "kernel_ms": {k: statistics.median(v) for k, v in phases.items()},
             "step_frac_of_peak": value / (peak_gbs * world)}
 
-
     # ---- end to end through the public API with host buffers
     e2e = None
-    if router_w is None:      # (the end-to-end leg is the step with logits as a host input)
+    if with_e2e and router_w is None:
         # okc.HostStep: pinned host inputs -> device, the step, result -> pinned host memory, captured
         # once per routing seed in a CUDA graph (one launch per step); the host waits for every step
         host_out = torch.empty((t1 - t0, wl.hidden), dtype=torch.bfloat16).pin_memory()
@@ -475,7 +520,7 @@ def run_gpu(args):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(args.steps):
+        for i in range(steps):
             e2e_step(i)
         e1.record()
         torch.cuda.synchronize()
@@ -484,63 +529,144 @@ def run_gpu(args):
             t = torch.tensor([e_ms], dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e_ms = float(t.item())
-        e2e = {"value": step_bytes / (e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e_ms / args.steps,
+        e2e = {"value": step_bytes / (e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e_ms / steps,
                "h2d_bytes_per_step": (t1 - t0) * wl.hidden * 2 + (t1 - t0) * wl.n_experts * 4,
                "d2h_bytes_per_step": (t1 - t0) * wl.hidden * 2}
+        del host_steps
 
-    # ---- CPU baseline (rank 0, N = 1 only): the oracle on a bounded sample of the same step
+    # ---- parity of one step (outside every timed region): this rank's output rows against the oracle
+    parity = None
+    if with_parity and router_w is None:
+        h, lg = inputs[0]
+        if world == 1:
+            out_rows = okc.moe_step(h, lg, state).clone()
+        else:
+            dist.barrier()
+            out_rows = layer.step(h[t0:t1].contiguous(), lg[t0:t1].contiguous()).clone()
+        torch.cuda.synchronize()
+        parity = _parity(wl, h, lg, out_rows, t0, state["ids"][:tokens], dev, n_tokens=4 if world == 1 else 2)
+        if world > 1:
+            allp = [None] * world
+            dist.all_gather_object(allp, parity)
+            parity = {"ok": all(p["ok"] for p in allp), "ids_exact": all(p["ids_exact"] for p in allp),
+                      "max_abs": max(p["max_abs"] for p in allp), "rel_l2": max(p["rel_l2"] for p in allp),
+                      "tokens": sum(p["tokens"] for p in allp)}
+
+    graphs.clear()
+    return {"value": value, "ms_per_step": ms_per_step, "step_bytes": step_bytes, "touched": touched, "timing": timing,
+            "roofline": roof, "e2e": e2e, "parity": parity, "clocks": clocks, "per_rank": per_rank, "state": state,
+            "layer": layer, "times_ms": times_ms, "t0": t0, "t1": t1, "bytes_seed0": bytes_per_seed[0], "inputs0": inputs[0],
+            "router": "logits = hidden . router_w^T computed inside the step" if router_w is not None else "logits given"}
+
+
+def _cpu_baseline(wl, tokens, hidden, logits, step_bytes, dev):
+    """The oracle (torch CPU operators, all host cores) on one whole step of the workload: every
+    touched expert of routing seed 0, once after a one-expert warm-up."""
+    import torch
+    from oracle import moe_torch
+    torch.set_num_threads(os.cpu_count() or 1)
+    hc, lc = hidden.cpu(), logits.cpu()
+    ids_o, w_o = moe_torch.route_softmax_topk(lc, wl.top_k)
+    touched = sorted(int(e) for e in torch.unique(ids_o).tolist())
+    by = {e: _cpu_expert(wl, e, dev) for e in touched}
+    wn = {k: _IndexByExpert(by, k, wl.n_experts) for k in _KEYS}
+    moe_torch.experts(hc, ids_o, w_o, wn, only_experts={touched[0]})          # warm-up
+    c0 = time.perf_counter()
+    moe_torch.experts(hc, ids_o, w_o, wn).to(torch.bfloat16)
+    dt = time.perf_counter() - c0
+    return {"value": step_bytes / dt / 1e9, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "seconds_per_step": dt,
+            "sample": f"one whole step: all {len(touched)} touched experts of routing seed {SEEDS[0]} "
+                      "(torch CPU dequantise + 2 FP32 matmuls each), timed once after a warm-up"}
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from okc_muse_kernels_b200 import _lib, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    wl = synth.WORKLOADS[args.workload or ("c2" if world == 1 else "c4")]
+    tokens = args.tokens or wl.tokens
+    m = measure(wl, tokens, args, dev, world, rank, max_tokens=max(synth.C3_TOKENS) if args.sweep else None)
+    failed = m["parity"] is not None and not m["parity"]["ok"]
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        torch.set_num_threads(os.cpu_count() or 1)
-        h, lg = inputs[0]
-        n_sample = 8
-        from oracle import moe_torch
-        hc, lc = h.cpu(), lg.cpu()
-        ids_o, w_o = moe_torch.route_softmax_topk(lc, wl.top_k)
-        sample = sorted(int(e) for e in torch.unique(ids_o).tolist())[:n_sample]
-        keys = ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs")
-        sub = {e: {k: v.cpu() for k, v in synth.make_weights(wl, device=dev, n_experts=1, first_expert=e).items()}
-               for e in sample}
-        wn = {k: _IndexByExpert({e: sub[e][k][0] for e in sample}, wl.n_experts) for k in keys}
-        moe_torch.experts(hc, ids_o, w_o, wn, only_experts={sample[0]})          # warm-up
-        c0 = time.perf_counter()
-        moe_torch.experts(hc, ids_o, w_o, wn, only_experts=set(sample))
-        dt = time.perf_counter() - c0
-        full_s = dt * touched[0] / len(sample)
-        cpu = {"value": bytes_per_seed[0] / full_s / 1e9, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-               "seconds_per_step": full_s,
-               "sample": f"{len(sample)} of {touched[0]} touched experts of one step (torch CPU dequantise + 2 FP32 matmuls each), scaled to the step"}
+        h, lg = m["inputs0"]
+        cpu = _cpu_baseline(wl, tokens, h, lg, m["bytes_seed0"], dev)
+
+    extra = {}
+    if world == 1 and args.workload is None and args.tokens is None and not args.no_c4_anchor and not args.sweep:
+        # configuration 4 on this one GPU (all 256 experts + the shared expert local, no exchange): the
+        # N = 1 point of the curve whose N = 2, 4, 8 points are the expert-parallel runs
+        state = m.pop("state")
+        del state
+        torch.cuda.empty_cache()
+        c4 = synth.WORKLOADS["c4"]
+        a = measure(c4, c4.tokens, args, dev, 1, 0, with_e2e=False, with_clocks=False, steps=min(args.steps, 50))
+        extra["c4_n1"] = {"workload": _workload_name(c4, c4.tokens, 1), "ms_per_step": a["ms_per_step"], "value": a["value"],
+                          "unit": UNIT, "touched_experts_per_seed": a["touched"], "gemm_ms": a["roofline"]["kernel_ms"]["gemm"],
+                          "frac_of_peak": a["roofline"]["step_frac_of_peak"], "parity": a["parity"]}
+        failed = failed or not a["parity"]["ok"]
+    if args.sweep:
+        # configuration 3: the batch sweep on configuration 2's weights, one entry per T
+        rows = []
+        for t in synth.C3_TOKENS:
+            a = measure(wl, t, args, dev, 1, 0, state=m["state"], with_e2e=False, with_clocks=False, steps=min(args.steps, 50))
+            rows.append({"tokens": t, "ms_per_step": a["ms_per_step"], "value": a["value"],
+                         "frac_of_peak": a["roofline"]["step_frac_of_peak"], "touched_experts_per_seed": a["touched"],
+                         "gemm_ms": a["roofline"]["kernel_ms"]["gemm"], "gemm_frac": a["roofline"]["frac"], "parity": a["parity"]})
+            failed = failed or not a["parity"]["ok"]
+        extra["sweep"] = rows
 
     # kernels of this library per step beyond the single-GPU step's: the token push and, unless the
     # combine is fused with the reduce-scatter, the pull-reduce (peer exchange); the cast (NCCL exchange)
+    layer = m["layer"]
     ep_extra_launches = 0
     if world > 1:
         ep_extra_launches = (1 if layer.fuse_combine else 2) if layer.exchange == "peer" else 1
     if rank == 0:
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms_per_step, "us_per_step": 1e3 * ms_per_step, "higher_is_better": True,
+        line = {"metric": METRIC, "value": m["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": m["ms_per_step"], "higher_is_better": True,
                 "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": _workload_name(wl, tokens, world),
-                           "l2": "touched weights per step exceed L2 (126 MB) and a 256 MB buffer is read between timed steps",
-                           "timing": "CUDA-graph replay per step" if world == 1 else ep_timing,
-                           "router": "logits = hidden . router_w^T computed inside the step" if router_w is not None else "logits given",
-                           "touched_experts_per_seed": touched, "routing_seeds": list(SEEDS)},
-                "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-                "gpu_launches": (_lib.lib().okc_moe_launches_per_step() + ep_extra_launches) * args.steps,
-                "step_ms_median": statistics.median(times_ms), "step_ms_min": min(times_ms)}
+                "config": _config(wl, tokens, world),
+                "detail": {"timing": m["timing"], "router": m["router"], "touched_experts_per_seed": m["touched"],
+                           "us_per_step": 1e3 * m["ms_per_step"], "step_ms_median": statistics.median(m["times_ms"]),
+                           "step_ms_min": min(m["times_ms"])},
+                "roofline": m["roofline"], "cpu_baseline": cpu, "e2e": m["e2e"], "parity": m["parity"], "clocks": m["clocks"],
+                "gpu_launches": (_lib.lib().okc_moe_launches_per_step() + ep_extra_launches) * args.steps}
+        if m["per_rank"] is not None:
+            line["per_rank"] = m["per_rank"]
+        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
-        captured = True      # the end-to-end leg always captures the step (okc.HostStep)
-        graphs.clear()
         torch.cuda.synchronize()
         dist.barrier()
-        if captured:
-            # tearing down a communicator whose collectives were captured in CUDA graphs was seen to
-            # block; every rank is past its last collective here, so leave without the teardown
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        if layer.exchange == "nccl":
+            # The graphs of this exchange hold captured NCCL kernels; destroying their communicator while
+            # such graphs were alive was seen to block once, and the cause was not found.  Every rank is
+            # past its last collective, so this (non-default) path leaves without the teardown.
+            os._exit(1 if failed else 0)
+        # default path: no collective was captured.  Tear the group down, but never wait for it for long.
+        watchdog = threading.Timer(30.0, lambda: os._exit(1 if failed else 0))
+        watchdog.daemon = True
+        watchdog.start()
         dist.destroy_process_group()
+        watchdog.cancel()
+    if failed:
+        raise SystemExit("parity check against the oracle failed (see the `parity` keys of the line)")
 
 
 def main():
@@ -552,12 +678,15 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "c1", "c2", "c4", "c5"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-c4-anchor", action="store_true", help="N = 1: skip the configuration-4 single-GPU step (`c4_n1`)")
+    ap.add_argument("--sweep", action="store_true", help="N = 1: add configuration 3 (T = 1 ... 256) as `sweep`")
     ap.add_argument("--route-from-hidden", action="store_true",
                     help="N = 1: compute the router logits from the token rows inside the step (okc.moe_layer_step)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the all-gather / reduce-scatter through this library's peer-memory kernels or NCCL")
     ap.add_argument("--ep-graphs", type=int, default=1, choices=[0, 1],
-                    help="N > 1: capture the expert-parallel step (kernels + NCCL collectives) in CUDA graphs")
+                    help="N > 1: capture the expert-parallel step (this library's kernels, and the NCCL collectives "
+                         "with --exchange nccl) in CUDA graphs")
     args = ap.parse_args()
     # a run that stops making progress prints every thread's stack and exits instead of hanging
     faulthandler.dump_traceback_later(int(os.environ.get("OKC_BENCH_WATCHDOG_S", "900")), exit=True)

@@ -174,7 +174,8 @@ int okc_moe_step(const okc_moe_plan* plan, const void* packed_w13, const void* p
  *    start at zero; everything else is overwritten by the step.  Two calls whose kernels overlap
  *    on the GPU (different streams, or a graph replay racing a direct call) corrupt each other:
  *    keep them on one stream or otherwise serialised.
- *  - The status word of this variant lives in the array, so okc_moe_read_status cannot reach it.
+ *  - The status word of this variant lives in the array, so okc_moe_read_status cannot reach it:
+ *    okc_moe_read_status_static reads it (before the next call of this entry point, which clears it).
  * All other arguments are those of okc_moe_step.
  */
 #define OKC_MOE_STATIC_SCRATCH_BYTES (32u << 20)
@@ -183,6 +184,11 @@ int okc_moe_step_static_scratch(const okc_moe_plan* plan, const void* packed_w13
                                 int64_t hidden_stride, const float* logits, int T, int own_t0, int own_t1,
                                 const void* post_norm_w, int32_t* ids, float* weights, void* out,
                                 int out_f32, okc_stream_t stream);
+
+/* okc_moe_read_status for the array of okc_moe_step_static_scratch on the current device:
+ * synchronises `stream`, returns 0 or OKC_ERR_TIMEOUT with *detail naming the wait that ran out.
+ * (No counterpart in the reference.) */
+int okc_moe_read_status_static(okc_stream_t stream, int32_t* detail);
 
 /*
  * The exchange steps of the expert-parallel layer over peer memory (NVLink / NVSwitch), for one
@@ -199,7 +205,7 @@ int okc_moe_step_static_scratch(const okc_moe_plan* plan, const void* packed_w13
  *  - okc_ep_reduce_scatter: out_bf16 [T/world, H] = sum over ranks (rank order) of their partial
  *    rows of this rank's tokens, rounded once.
  * All ranks must make the same calls in the same order.  The waits on other ranks are bounded (five
- * seconds); one that runs out is reported by okc_ep_read_status (OKC_ERR_TIMEOUT, detail 0x100 + rank
+ * seconds, or okc_ep_comm.wait_limit_ms); one that runs out is reported by okc_ep_read_status (OKC_ERR_TIMEOUT, detail 0x100 + rank
  * for the gather, 0x200 + rank for the reduce) and the step's result is then undefined.
  */
 #define OKC_EP_MAX_RANKS 16
@@ -208,7 +214,8 @@ typedef struct okc_ep_comm {
   int32_t tokens;      /* T of the whole step, a multiple of world */
   int32_t hidden;      /* H, a multiple of 256 */
   int32_t n_experts;   /* E, a multiple of 4 */
-  int32_t reserved[3]; /* must be zero */
+  int32_t wait_limit_ms; /* limit of every wait on another rank in milliseconds; 0 = five seconds */
+  int32_t reserved[2];   /* must be zero */
   void* peer[OKC_EP_MAX_RANKS]; /* this process's address of rank r's buffer; peer[rank] is its own */
 } okc_ep_comm;
 
@@ -226,6 +233,12 @@ int okc_moe_experts_ep(const okc_moe_plan* plan, const void* packed_w13, const v
                        const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,
                        int T, void* workspace, const okc_ep_comm* comm, void* out_bf16,
                        okc_stream_t stream);
+/* Raises, in this rank's own buffer, the flag that rank `from_rank` raises when its token rows
+ * (which = 0) or its partial sums (which = 1) of the coming exchange are in place.  For a harness that
+ * runs the ranks of a step one after the other on one device (there the later rank's data is put in
+ * place by other means, and a kernel must never wait for a kernel launched after it).  No counterpart
+ * in the reference. */
+int okc_ep_mark_arrived(const okc_ep_comm* comm, int which, int from_rank, okc_stream_t stream);
 /* Synchronises `stream`; returns the status kept in this rank's buffer and clears it. */
 int okc_ep_read_status(const okc_ep_comm* comm, okc_stream_t stream, int32_t* detail);
 

@@ -40,7 +40,8 @@ EP_MAX_RANKS = 16
 class EpComm(C.Structure):
     """okc_ep_comm"""
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("tokens", C.c_int32), ("hidden", C.c_int32),
-                ("n_experts", C.c_int32), ("reserved", C.c_int32 * 3), ("peer", C.c_void_p * EP_MAX_RANKS)]
+                ("n_experts", C.c_int32), ("wait_limit_ms", C.c_int32), ("reserved", C.c_int32 * 2),
+                ("peer", C.c_void_p * EP_MAX_RANKS)]
 
 
 class Router(C.Structure):
@@ -69,6 +70,7 @@ SIGNATURES = {
                                _P, C.c_int, _P]),
     "okc_moe_step_static_scratch": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, _P, C.c_int, C.c_int, C.c_int, _P, _P,
                                               _P, _P, C.c_int, _P]),
+    "okc_moe_read_status_static": (C.c_int, [_P, C.POINTER(C.c_int32)]),
     "okc_moe_export_sort": (C.c_int, [_PLAN, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P]),
     "okc_moe_unpack_bf16": (C.c_int, [_PLAN, _P, C.c_int, C.c_int, _P, _P]),
     "okc_moe_probe_wait_timeout": (C.c_int, [_P, _P]),
@@ -78,6 +80,7 @@ SIGNATURES = {
     "okc_ep_gather_tokens": (C.c_int, [_COMM, _P, C.c_int64, _P, _P]),
     "okc_ep_reduce_scatter": (C.c_int, [_COMM, _P, _P]),
     "okc_moe_experts_ep": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _COMM, _P, _P]),
+    "okc_ep_mark_arrived": (C.c_int, [_COMM, C.c_int, C.c_int, _P]),
     "okc_ep_read_status": (C.c_int, [_COMM, _P, C.POINTER(C.c_int32)]),
 }
 

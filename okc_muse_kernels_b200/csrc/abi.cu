@@ -41,15 +41,6 @@ static bool encode_rows_map(CUtensorMap* map, void* base, uint64_t rows, uint64_
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-#ifdef OKC_WAIT_PROFILE
-static std::atomic<int> g_dbg_flags{0};
-#define OKC_DBG_FLAGS g_dbg_flags.load()
-#define OKC_DBG_SPLIT ((g_dbg_flags.load() >> 8) & 1)
-#else
-#define OKC_DBG_FLAGS 0
-#define OKC_DBG_SPLIT 0
-#endif
-
 static int ncap_for(const okc_moe_plan* plan, int T) { return chunk_rows_for(T, plan->top_k, plan->n_experts); }
 
 static int sm_count() {
@@ -142,12 +133,6 @@ using namespace okc;
 extern "C" {
 
 int okc_moe_version(void) { return 101; }
-
-#ifdef OKC_WAIT_PROFILE
-// Experiment switches of the instrumented build: bit 0 skip the dequantisation arithmetic, bit 1 skip
-// the MMAs, bit 2 skip the tensor-memory stores.  Results are wrong with any of them set.
-int okc_moe_debug_set_flags(int flags) { g_dbg_flags.store(flags); return 0; }
-#endif
 
 const char* okc_moe_strerror(int code) {
   switch (code) {
@@ -282,17 +267,9 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   a.meta = w.meta; a.items = w.items; a.done = w.done;
   a.ncap = ncap; a.n_stages = gemm_stages_for(ncap);
   a.inter = w.inter; a.I = g.I; a.H = g.H; a.y = w.y; a.sorted = w.sorted; a.wsorted = w.wsorted;
-  a.weighted = plan->post_norm ? 0 : 1; a.dbg = OKC_DBG_FLAGS;
-  if (!OKC_DBG_SPLIT) {
-    a.phase_lo = 0; a.phase_hi = 1; a.work_counter = w.meta + kMetaWorkFused;
-    if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
-  } else {
-    // measurement only: one launch per phase
-    a.phase_lo = 0; a.phase_hi = 0; a.work_counter = w.meta + kMetaWorkPhase0;
-    if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
-    a.phase_lo = 1; a.phase_hi = 1; a.work_counter = w.meta + kMetaWorkPhase1;
-    if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
-  }
+  a.weighted = plan->post_norm ? 0 : 1;
+  a.phase_lo = 0; a.phase_hi = 1; a.work_counter = w.meta + kMetaWorkFused;
+  if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
   if (ev && cudaEventRecord(ev[2], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
   CombineParams c;
@@ -400,9 +377,9 @@ static bool ep_params(const okc_ep_comm* c, EpParams& p) {
   if (!c || c->world < 1 || c->world > kEpMaxRanks || c->rank < 0 || c->rank >= c->world) return false;
   if (c->tokens <= 0 || (c->tokens % c->world) != 0 || c->hidden <= 0 || (c->hidden % 256) != 0) return false;
   if (c->n_experts <= 0 || (c->n_experts % 4) != 0) return false;
-  for (int i = 0; i < 3; ++i)
-    if (c->reserved[i] != 0) return false;
+  if (c->wait_limit_ms < 0 || c->reserved[0] != 0 || c->reserved[1] != 0) return false;
   memset(&p, 0, sizeof(p));
+  p.wait_ns = c->wait_limit_ms > 0 ? 1000000ull * static_cast<unsigned long long>(c->wait_limit_ms) : 5000000000ull;
   for (int r = 0; r < c->world; ++r) {
     if (!c->peer[r] || !aligned(c->peer[r], 256)) return false;
     p.peer[r] = static_cast<uint8_t*>(c->peer[r]);
@@ -444,6 +421,14 @@ int okc_ep_reduce_scatter(const okc_ep_comm* comm, void* out_bf16, okc_stream_t 
   if (!out_bf16 || !aligned(out_bf16, 8)) return OKC_ERR_BAD_ARG;
   p.out = static_cast<uint16_t*>(out_bf16);
   return launch_ep_reduce(p, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+int okc_ep_mark_arrived(const okc_ep_comm* comm, int which, int from_rank, okc_stream_t stream) {
+  EpParams p;
+  if (!ep_params(comm, p)) return OKC_ERR_BAD_ARG;
+  if ((which != 0 && which != 1) || from_rank < 0 || from_rank >= p.world) return OKC_ERR_BAD_ARG;
+  return launch_ep_mark_arrived(p, which, from_rank, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK
+                                                                                                            : OKC_ERR_CUDA;
 }
 
 int okc_moe_experts_ep(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
@@ -519,6 +504,16 @@ int okc_moe_step_static_scratch(const okc_moe_plan* plan, const void* packed_w13
     return OKC_ERR_CUDA;
   return okc_moe_step(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, logits, T, own_t0, own_t1,
                       post_norm_w, ids, weights, scratch, out, out_f32, stream);
+}
+
+// The status words of the last okc_moe_step_static_scratch on the current device (they live in the
+// library's array, out of okc_moe_read_status' reach).  Read them before the next call of that
+// entry point: it clears them.
+int okc_moe_read_status_static(okc_stream_t stream, int32_t* detail) {
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != OKC_OK) return rc;
+  return okc_moe_read_status(scratch, stream, detail);
 }
 
 }  // extern "C"

@@ -21,8 +21,9 @@
 // its push_tokens of step n+1 saw every rank's step-n+1 flag, which a rank raises after its
 // pull_reduce of step n, i.e. after its last read of anybody's step-n partial sums.
 //
-// Every wait is bounded (kEpWaitNs of wall time); a wait that runs out records a code in the
-// buffer's status words and the kernel carries on to its end: nothing traps.
+// Every wait is bounded (five seconds of wall time unless the caller's okc_ep_comm gives a shorter
+// limit); a wait that runs out records a code in the buffer's status words and the kernel carries on
+// to its end: nothing traps.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -35,7 +36,6 @@ namespace okc {
 
 namespace {
 
-constexpr unsigned long long kEpWaitNs = 5000000000ull;   // 5 s: peers may start a step late
 
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
@@ -59,8 +59,8 @@ __device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* p) {
   return v;
 }
 
-// Waits until *flag >= want.  Returns false after kEpWaitNs.
-__device__ __forceinline__ bool wait_flag(const int32_t* flag, int32_t want) {
+// Waits until *flag >= want.  Returns false after limit_ns of wall time.
+__device__ __forceinline__ bool wait_flag(const int32_t* flag, int32_t want, unsigned long long limit_ns) {
   if (ld_acquire_sys(flag) >= want) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
@@ -68,7 +68,7 @@ __device__ __forceinline__ bool wait_flag(const int32_t* flag, int32_t want) {
       if (ld_acquire_sys(flag) >= want) return true;
       __nanosleep(200);
     }
-    if (global_ns() - t0 > kEpWaitNs) return false;
+    if (global_ns() - t0 > limit_ns) return false;
   }
 }
 
@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) okc_ep_push_tokens(const EpParams p) {
   const int32_t seq = ctrl[kEpCtrlSeqIn] + 1;
   if (threadIdx.x < p.world) {
     st_release_sys(flags_in_of(p.peer[threadIdx.x]) + p.rank, seq);
-    if (!wait_flag(flags_in_of(mine) + threadIdx.x, seq)) {
+    if (!wait_flag(flags_in_of(mine) + threadIdx.x, seq, p.wait_ns)) {
       atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
       atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x100 | threadIdx.x);
     }
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(256) okc_ep_pull_reduce(const EpParams p) {
     st_release_sys(flags_rs_of(p.peer[threadIdx.x]) + p.rank, seq);
   }
   if (threadIdx.x < p.world) {
-    if (!wait_flag(flags_rs_of(mine) + threadIdx.x, seq)) {
+    if (!wait_flag(flags_rs_of(mine) + threadIdx.x, seq, p.wait_ns)) {
       atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
       atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x200 | threadIdx.x);
     }
@@ -165,20 +165,24 @@ __global__ void __launch_bounds__(256) okc_ep_pull_reduce(const EpParams p) {
 }
 
 // The per-token combine of the local experts' outputs and the reduce-scatter in one kernel.
-// grid (H / 1024, T); the rows this rank owns are the last block rows, so that by the time their
-// CTAs wait for the other ranks, every CTA that only has to publish a partial row has been started.
+// grid (H / 1024, T); the rows this rank owns are the last block rows.
 //   every row t:   acc = sum over the token's local routes (slot order) of y[t * kk + slot]
-//   row of a peer: store acc into this rank's partial sums (the owner will load it)
-//   own row:       wait until every rank has published its partial sums, add them in rank order
+//   row of a peer: store acc into this rank's partial sums (the owner will load it); the CTA that is
+//                  last to publish raises this rank's flag on every rank
+//   own row:       wait until every other rank has published its partial sums, add them in rank order
 //                  (this rank's acc in its place), round once to bf16
-// The CTA that is last to finish the first part raises this rank's flag on every rank.
+// Only the publishing CTAs are counted towards the flag, and they never wait, so the kernel does not
+// need all of its CTAs resident at once: CTAs are handed to the SMs in block order, the publishing
+// ones (lower block rows) therefore all run before an own-row CTA can be left waiting for a free SM.
+// A second counter over all CTAs tells the one that finishes last to reset both counters and to
+// advance the step count (every CTA has read it by then).
 __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, const CombineParams c) {
   griddep_wait();    // y comes from the GEMM launch before
   uint8_t* mine = p.peer[p.rank];
   int32_t* ctrl = ctrl_of(mine);
   const int tb = p.tokens / p.world;
   const int own_t0 = p.rank * tb, own_t1 = own_t0 + tb;
-  const int32_t seq = ctrl[kEpCtrlSeqRs] + 1;   // changed only after every CTA has read it
+  const int32_t seq = ctrl[kEpCtrlSeqRs] + 1;
   int t = static_cast<int>(blockIdx.y) + own_t1;
   if (t >= p.tokens) t -= p.tokens;
   const bool own = t >= own_t0 && t < own_t1;
@@ -192,47 +196,69 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
       const float4 a = *reinterpret_cast<const float4*>(c.y + static_cast<size_t>(t * c.kk + s) * p.H + col);
       acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
     }
-    if (!own)
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(mine + p.off_partial) + static_cast<size_t>(t) * p.H + col) = acc;
   }
-  __threadfence_system();
-  __syncthreads();
-  __shared__ int s_last;
+  if (!own) {
+    if (live)
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(mine + p.off_partial) + static_cast<size_t>(t) * p.H + col) = acc;
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (threadIdx.x == 0) {
+      const int publishers = gridDim.x * (p.tokens - tb);
+      s_last = (atomicAdd(&ctrl[kEpCtrlDoneRs], 1) == publishers - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      // every publishing CTA of this rank has stored (and fenced) its rows
+      __threadfence_system();
+      if (threadIdx.x < p.world) st_release_sys(flags_rs_of(p.peer[threadIdx.x]) + p.rank, seq);
+    }
+  } else {
+    if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+      if (!wait_flag(flags_rs_of(mine) + threadIdx.x, seq, p.wait_ns)) {
+        atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
+        atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x300 | threadIdx.x);
+      }
+    }
+    __syncthreads();
+    if (live) {
+      const size_t off = static_cast<size_t>(t) * p.H + col;
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < p.world; ++r) {       // rank order: the same sum on every run
+        float4 v = acc;
+        if (r != p.rank) v = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r] + p.off_partial) + off);
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      }
+      __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(p.out + static_cast<size_t>(t - own_t0) * p.H + col) = o;
+    }
+  }
+  __syncthreads();   // every thread of the CTA has read the step count
   if (threadIdx.x == 0) {
     const int total = gridDim.x * gridDim.y;
-    s_last = (atomicAdd(&ctrl[kEpCtrlDoneRs], 1) == total - 1) ? 1 : 0;
-  }
-  __syncthreads();
-  if (s_last) {
-    // every CTA of this rank has published (and fenced) its rows
-    __threadfence_system();
-    if (threadIdx.x < p.world) st_release_sys(flags_rs_of(p.peer[threadIdx.x]) + p.rank, seq);
-    if (threadIdx.x == 0) {
+    if (atomicAdd(&ctrl[kEpCtrlDoneAll], 1) == total - 1) {
       ctrl[kEpCtrlDoneRs] = 0;
+      ctrl[kEpCtrlDoneAll] = 0;
       ctrl[kEpCtrlSeqRs] = seq;
     }
   }
-  if (!own) return;
-  if (threadIdx.x < p.world && threadIdx.x != p.rank) {
-    if (!wait_flag(flags_rs_of(mine) + threadIdx.x, seq)) {
-      atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
-      atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x300 | threadIdx.x);
-    }
-  }
-  __syncthreads();
-  if (!live) return;
-  const size_t off = static_cast<size_t>(t) * p.H + col;
-  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int r = 0; r < p.world; ++r) {       // rank order: the same sum on every run
-    float4 v = acc;
-    if (r != p.rank) v = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r] + p.off_partial) + off);
-    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-  }
-  __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
-  uint2 o;
-  o.x = *reinterpret_cast<uint32_t*>(&lo);
-  o.y = *reinterpret_cast<uint32_t*>(&hi);
-  *reinterpret_cast<uint2*>(p.out + static_cast<size_t>(t - own_t0) * p.H + col) = o;
+}
+
+// One thread: the flag rank `from` raises on this rank when its part of the coming exchange is in
+// place (which = 0 token rows, 1 partial sums), at the value this rank's next wait expects.
+__global__ void okc_ep_mark_arrived(const EpParams p, int which, int from) {
+  uint8_t* mine = p.peer[p.rank];
+  const int32_t* ctrl = ctrl_of(mine);
+  if (which == 0) st_release_sys(flags_in_of(mine) + from, ctrl[kEpCtrlSeqIn] + 1);
+  else st_release_sys(flags_rs_of(mine) + from, ctrl[kEpCtrlSeqRs] + 1);
+}
+
+cudaError_t launch_ep_mark_arrived(const EpParams& p, int which, int from, cudaStream_t stream) {
+  okc_ep_mark_arrived<<<1, 1, 0, stream>>>(p, which, from);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_ep_push(const EpParams& p, cudaStream_t stream) {

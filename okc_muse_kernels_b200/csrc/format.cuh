@@ -92,7 +92,8 @@ inline bool make_geometry(const okc_moe_plan& p, Geometry& g) {
 // the gathered token rows, the gathered router logits and this rank's FP32 partial sums.
 constexpr int kEpMaxRanks = OKC_EP_MAX_RANKS;
 constexpr size_t kEpOffFlagsIn = 256, kEpOffFlagsRs = 512, kEpOffData = 1024;
-enum EpCtrlWord { kEpCtrlSeqIn = 0, kEpCtrlSeqRs = 1, kEpCtrlDoneIn = 2, kEpCtrlDoneRs = 3, kEpCtrlStatus = 4, kEpCtrlDetail = 5 };
+enum EpCtrlWord { kEpCtrlSeqIn = 0, kEpCtrlSeqRs = 1, kEpCtrlDoneIn = 2, kEpCtrlDoneRs = 3, kEpCtrlStatus = 4, kEpCtrlDetail = 5,
+                  kEpCtrlDoneAll = 6 };
 struct EpLayout {
   size_t off_hidden, off_logits, off_partial, total;
 };

@@ -60,10 +60,8 @@ __device__ long long g_wait_prof[kProfCtas][kProfSlots];
 #define OKC_PROF_DECL long long prof_acc[kProfSlots] = {0}; const long long prof_t0 = clock64();
 #define OKC_PROF_WAIT(idx, expr) ([&] { const long long _t = clock64(); const bool _r = (expr); prof_acc[idx] += clock64() - _t; return _r; }())
 #define OKC_PROF_VOID(idx, stmt) { const long long _t = clock64(); stmt; prof_acc[idx] += clock64() - _t; }
-#define OKC_DBG(bit) ((p.dbg >> (bit)) & 1)
 #define OKC_PROF_STORE(idx_total, lo, hi) { prof_acc[idx_total] = clock64() - prof_t0; if (blockIdx.x < kProfCtas) for (int _i = lo; _i <= hi; ++_i) g_wait_prof[blockIdx.x][_i] = prof_acc[_i]; }
 #else
-#define OKC_DBG(bit) 0
 #define OKC_PROF_DECL
 #define OKC_PROF_WAIT(idx, expr) (expr)
 #define OKC_PROF_VOID(idx, stmt) { stmt; }
@@ -95,6 +93,7 @@ struct Ctrl {
   uint64_t u_full[kURing];          // unit descriptor published
   uint64_t u_empty[kURing];         // every consumer warp has read it
   uint64_t dummy;                   // arrived on, never waited on
+  uint64_t drain[kIssuers];         // an issuer that gives up waits here for the MMAs it has in flight
   UnitDesc units[kURing];
   uint32_t tmem_base;
   int abort_code;
@@ -156,6 +155,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
       mbar_init(bar_uempty + 8 * i, kUnitConsumers);
     }
     mbar_init(smem_u32(&ctrl->dummy), 1);
+    for (int i = 0; i < kIssuers; ++i) mbar_init(smem_u32(&ctrl->drain[i]), 1);
     ctrl->abort_code = 0;
     mbar_fence_init();
   }
@@ -305,12 +305,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
           const uint32_t lo = (desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4)) + kb_off;
           if (!OKC_PROF_WAIT(4, mbar_wait(my_afull, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
           tc_fence_after();
-          if (!OKC_DBG(1)) {
-            mma_ts2(d, a0, lo, desc_hi, idesc, acc);
-            mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
-            mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
-            mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
-          }
+          mma_ts2(d, a0, lo, desc_hi, idesc, acc);
+          mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
+          mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
+          mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
           acc = 1;
           mma_commit(my_aempty);
           mma_commit(bar_empty + 8 * st);
@@ -320,6 +318,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
         mma_commit(bar_accfull + 8 * buf);
       }
     issuer_done:
+      if (*abort_flag != 0) {
+        // giving up: the MMAs already issued still read the A ring and write the accumulators, so
+        // tensor memory may only be freed once they have retired (bounded, like the producer's drain)
+        const uint32_t bar = smem_u32(&ctrl->drain[warp]);
+        mma_commit(bar);
+        const long long t0 = clock64();
+        while (!mbar_try(bar, 0) && clock64() - t0 < kWaitLimitCycles) {}
+      }
       if (warp == 0) { OKC_PROF_STORE(5, 2, 5) }
     }
   } else if (warp >= kDequantWarp0 && warp < kDequantWarp0 + kDequantWarps) {
@@ -358,12 +364,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
             const uint32_t sp1 = sp0 + kTileRows * 2;
             const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
             uint32_t r[16];
-            if (!OKC_DBG(0)) {
-              dequant_chunk(w0, s00, s01, r);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) r[i] = w0.x ^ s00;
-            }
+            dequant_chunk(w0, s00, s01, r);
             // the stores of the previous slot completed while this chunk was being dequantised:
             // only now wait for them and hand that slot to its MMA issuer
             OKC_PROF_VOID(8, tmem_wait_st())
@@ -373,18 +374,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
             // in all of them and the warp stays converged for the tensor-memory stores below
             if (!OKC_PROF_WAIT(7, mbar_wait(my_aempty + 16 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) goto dq_done;
             tc_fence_after();
-            if (!OKC_DBG(2)) tmem_st16(trow + kb * kASlotCols, r);
-            if (!OKC_DBG(0)) {
-              dequant_chunk(w1, s10, s11, r);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) r[i] = w1.y ^ s10;
-            }
-            if (!OKC_DBG(2)) {
-              tmem_st16(trow + kb * kASlotCols + 16, r);
-            } else if (r[3] == 0x12345678u) {
-              p.y[0] = 1.0f;   // keeps the registers alive
-            }
+            tmem_st16(trow + kb * kASlotCols, r);
+            dequant_chunk(w1, s10, s11, r);
+            tmem_st16(trow + kb * kASlotCols + 16, r);
             pend_bar = my_afull + 16 * kb;
           }
         }

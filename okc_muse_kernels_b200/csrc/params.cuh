@@ -78,7 +78,6 @@ struct MoeGemmParams {
   const float* wsorted;
   int H;
   int weighted;
-  int dbg;   // experiment switches, honoured only by the -DOKC_WAIT_PROFILE build (0 otherwise)
 };
 cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream);
 int gemm_stages_for(int ncap);
@@ -92,9 +91,11 @@ struct EpParams {
   int64_t hidden_stride;
   const float* logits_own;      // push: f32 [tokens / world, E]
   uint16_t* out;                // reduce: bf16 [tokens / world, H]
+  unsigned long long wait_ns;   // limit of every wait on another rank
 };
 cudaError_t launch_ep_push(const EpParams& p, cudaStream_t stream);
 cudaError_t launch_ep_reduce(const EpParams& p, cudaStream_t stream);
+cudaError_t launch_ep_mark_arrived(const EpParams& p, int which, int from, cudaStream_t stream);
 
 struct CombineParams {
   const float* y;

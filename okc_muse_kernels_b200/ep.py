@@ -26,7 +26,9 @@ Two implementations of steps 1 and 3 + 4:
 from __future__ import annotations
 
 import ctypes as C
+import datetime
 import os
+import time
 from typing import Callable
 
 import torch
@@ -77,42 +79,71 @@ def _map_with_symmetric_memory(nbytes: int, group, device):
 
 
 class PeerExchange:
-    """The ranks' exchange buffers, each mapped into every rank (torch's symmetric-memory allocator:
-    cuMemCreate + cuMemMap with access for every GPU of the group), and the two exchange kernels.
-    Raises RuntimeError on every rank if the buffers cannot be mapped."""
+    """The ranks' exchange buffers, each mapped into every rank, and the exchange kernels.
 
-    def __init__(self, tokens: int, hidden: int, n_experts: int, group=None, device=None):
+    The default constructor takes the buffers from torch's symmetric-memory allocator (cuMemCreate +
+    cuMemMap with access for every GPU of the group) and raises RuntimeError on every rank if they
+    cannot be mapped.  ``from_buffers`` takes addresses the caller already has (any peer mapping; or
+    several buffers on one device, for a harness that runs the ranks one after the other).
+    ``wait_limit_ms`` bounds every wait on another rank (0: five seconds)."""
+
+    def __init__(self, tokens: int, hidden: int, n_experts: int, group=None, device=None, wait_limit_ms: int = 0):
         self.group = group
-        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        if self.world > _lib.EP_MAX_RANKS:
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world > _lib.EP_MAX_RANKS:
             raise ValueError(f"at most {_lib.EP_MAX_RANKS} ranks")
         device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
-        nbytes = int(_lib.lib().okc_ep_buffer_bytes(tokens, hidden, n_experts))
+        nbytes = self.buffer_bytes(tokens, hidden, n_experts)
         ok, why = 1, ""
+        buf, ptrs = None, []
         try:
-            self.buf, ptrs, self._keep = _map_with_symmetric_memory(nbytes, group, device)
+            buf, ptrs, self._keep = _map_with_symmetric_memory(nbytes, group, device)
         except Exception as exc:   # noqa: BLE001 - whatever went wrong, every rank must learn of it
             ok, why = 0, str(exc)
         flag = torch.tensor([ok], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
         if int(flag.item()) != 1:
             raise RuntimeError(f"the ranks' exchange buffers could not be mapped into each other ({why or 'another rank failed'})")
-        self.comm = _lib.EpComm(rank=self.rank, world=self.world, tokens=tokens, hidden=hidden, n_experts=n_experts)
+        self._setup(rank, world, tokens, hidden, n_experts, buf, ptrs, wait_limit_ms)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)     # every buffer is zeroed and mapped before anybody's first step
+
+    @staticmethod
+    def buffer_bytes(tokens: int, hidden: int, n_experts: int) -> int:
+        n = int(_lib.lib().okc_ep_buffer_bytes(tokens, hidden, n_experts))
+        if n == 0:
+            raise ValueError("bad exchange-buffer shape")
+        return n
+
+    @classmethod
+    def from_buffers(cls, rank: int, world: int, tokens: int, hidden: int, n_experts: int, own: torch.Tensor,
+                     ptrs: list[int], wait_limit_ms: int = 0) -> "PeerExchange":
+        """``own``: this rank's zeroed uint8 buffer of ``buffer_bytes`` bytes; ``ptrs[r]``: the address
+        under which this process reaches rank r's buffer (``ptrs[rank] == own.data_ptr()``)."""
+        self = cls.__new__(cls)
+        self.group = None
+        self._setup(rank, world, tokens, hidden, n_experts, own, ptrs, wait_limit_ms)
+        return self
+
+    def _setup(self, rank, world, tokens, hidden, n_experts, buf, ptrs, wait_limit_ms):
+        if len(ptrs) != world or ptrs[rank] != buf.data_ptr():
+            raise ValueError("ptrs must hold one address per rank, the rank's own buffer at its own index")
+        self.world, self.rank, self.buf = world, rank, buf
+        self.comm = _lib.EpComm(rank=rank, world=world, tokens=tokens, hidden=hidden, n_experts=n_experts,
+                                wait_limit_ms=int(wait_limit_ms))
         for r, ptr in enumerate(ptrs):
             self.comm.peer[r] = ptr
         views = [C.c_void_p() for _ in range(3)]
         _lib.check(_lib.lib().okc_ep_views(C.byref(self.comm), *[C.byref(v) for v in views]), "okc_ep_views")
-        base = self.buf.data_ptr()
+        base = buf.data_ptr()
 
         def view(ptr, nelem, dtype, shape):
             off = ptr.value - base
-            return self.buf[off:off + nelem * torch.empty((), dtype=dtype).element_size()].view(dtype).view(shape)
+            return buf[off:off + nelem * torch.empty((), dtype=dtype).element_size()].view(dtype).view(shape)
 
         self.hidden_all = view(views[0], tokens * hidden, torch.bfloat16, (tokens, hidden))
         self.logits_all = view(views[1], tokens * n_experts, torch.float32, (tokens, n_experts))
         self.partial = view(views[2], tokens * hidden, torch.float32, (tokens, hidden))
-        torch.cuda.synchronize(device)
-        dist.barrier(group=group)     # every buffer is zeroed and mapped before anybody's first step
 
     def gather_tokens(self, hidden_own: torch.Tensor, logits_own: torch.Tensor) -> None:
         if hidden_own.stride(-1) != 1 or not logits_own.is_contiguous():
@@ -125,10 +156,97 @@ class PeerExchange:
         _lib.check(_lib.lib().okc_ep_reduce_scatter(C.byref(self.comm), out.data_ptr(),
                                                    torch.cuda.current_stream().cuda_stream), "okc_ep_reduce_scatter")
 
+    def mark_arrived(self, which: str, from_rank: int) -> None:
+        """Raises, in this rank's own buffer, the flag rank ``from_rank`` raises when its token rows
+        (``which="tokens"``) or its partial sums (``"partial"``) of the coming exchange are in place.
+        For a harness that runs the ranks of a step one after the other on one device: there the data
+        of the rank that runs later is put in place by other means, and no kernel may wait for a
+        kernel launched after it."""
+        _lib.check(_lib.lib().okc_ep_mark_arrived(C.byref(self.comm), {"tokens": 0, "partial": 1}[which], int(from_rank),
+                                                 torch.cuda.current_stream().cuda_stream), "okc_ep_mark_arrived")
+
     def read_status(self) -> tuple[int, int]:
         detail = C.c_int32(0)
         rc = _lib.lib().okc_ep_read_status(C.byref(self.comm), torch.cuda.current_stream().cuda_stream, C.byref(detail))
         return rc, detail.value
+
+    def reset(self) -> None:
+        """Zeroes this rank's buffer (step counts, flags, status).  After a wait that ran out the ranks'
+        step counts may differ: every rank resets, with a host-side barrier before and after, between
+        steps."""
+        self.buf.zero_()
+        torch.cuda.synchronize(self.buf.device)
+        if self.group is not None or (dist.is_available() and dist.is_initialized() and self.world > 1):
+            dist.barrier(group=self.group)
+
+
+class PeerLost(RuntimeError):
+    """A rank of the expert-parallel group left, or did not reach the step within the deadline."""
+
+
+class StepGuard:
+    """Host-side failure detection for the expert-parallel step: before a rank launches step n it
+    checks in through the process group's key-value store and waits, up to ``deadline_s``, until
+    every rank has checked in for step n.  A rank that leaves (``leave()``, between steps, nothing
+    in flight) or that is late makes the others raise ``PeerLost`` on the host before they launch
+    anything, so that no kernel or collective is left waiting for a rank that will not come.
+
+    The device-side waits of the exchange kernels are bounded as well, but a wait that runs out there
+    costs the step; this check costs a store round trip and keeps the GPU out of it."""
+
+    def __init__(self, store, rank: int, world: int, deadline_s: float = 5.0, prefix: str = "okc_ep"):
+        self.store, self.rank, self.world = store, rank, world
+        self.deadline = datetime.timedelta(seconds=deadline_s)
+        self.prefix = prefix
+        self.n = 0
+
+    def _key(self, kind: str, n, rank: int) -> str:
+        return f"{self.prefix}/{kind}/{n}/{rank}"
+
+    def check_in(self) -> int:
+        """Call before launching a step.  Returns the step number; raises PeerLost (and then counts
+        as gone itself, so that a rank that arrives late does not launch alone)."""
+        n = self.n
+        self.store.set(self._key("step", n, self.rank), "1")
+        others = [r for r in range(self.world) if r != self.rank]
+        keys = [self._key("step", n, r) for r in others]
+        t_end = time.monotonic() + self.deadline.total_seconds()
+        while True:
+            self._raise_if_gone(others, n)     # a rank that went is noticed at once, not at the deadline
+            try:
+                if not keys or self.store.check(keys):
+                    break
+            except Exception:      # noqa: BLE001 - a store that cannot answer: the deadline decides
+                pass
+            if time.monotonic() >= t_end:
+                msg = f"not every rank reached step {n} within {self.deadline.total_seconds():.1f} s"
+                self.leave(f"gave up on step {n}: {msg}")
+                raise PeerLost(msg)
+            time.sleep(0.002)
+        self.n = n + 1
+        return n
+
+    def _gone(self, r: int) -> str | None:
+        """What rank r said when it went (None: it is still there)."""
+        key = self._key("gone", "x", r)
+        try:
+            if not self.store.check([key]):
+                return None
+            return self.store.get(key).decode()
+        except Exception:          # noqa: BLE001 - a store that cannot answer: the deadline decides
+            return None
+
+    def _raise_if_gone(self, others, n) -> None:
+        for r in others:
+            why = self._gone(r)
+            if why is not None:
+                msg = f"rank {r} {why}"
+                self.leave(f"gave up on step {n}: {msg}")
+                raise PeerLost(msg)
+
+    def leave(self, why: str = "left") -> None:
+        """Call between steps, with none of this rank's kernels or collectives in flight."""
+        self.store.set(self._key("gone", "x", self.rank), why)
 
 
 class ExpertParallelMoE:
@@ -143,7 +261,8 @@ class ExpertParallelMoE:
 
     def __init__(self, plan: MoEPlan, tokens: int, weights: dict | None = None, group=None,
                  local_step: Callable | None = None, cast: Callable | None = None,
-                 device: torch.device | str | None = None, exchange: str = "nccl", fuse_combine: bool = True):
+                 device: torch.device | str | None = None, exchange: str = "nccl", fuse_combine: bool = True,
+                 guard: "StepGuard | None" = None, wait_limit_ms: int = 0):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -170,12 +289,14 @@ class ExpertParallelMoE:
         if exchange == "peer" and local_step is not None:
             raise ValueError("the peer-memory exchange runs on GPUs only")
         self.exchange = exchange
+        self.guard = guard
         # peer exchange: the combine and the reduce-scatter as one kernel (not with the post-expert
         # norm, which needs whole rows before the sum)
         self.fuse_combine = bool(fuse_combine and exchange == "peer" and not plan.post_norm)
         self.peer = None
         if exchange == "peer":
-            self.peer = PeerExchange(tokens, plan.hidden, plan.n_experts, group=group, device=device)
+            self.peer = PeerExchange(tokens, plan.hidden, plan.n_experts, group=group, device=device,
+                                     wait_limit_ms=wait_limit_ms)
             self.hidden_all, self.logits_all, self.partial = self.peer.hidden_all, self.peer.logits_all, self.peer.partial
         else:
             self.hidden_all = torch.empty((tokens, plan.hidden), dtype=torch.bfloat16, device=device)
@@ -189,7 +310,11 @@ class ExpertParallelMoE:
 
     def step(self, hidden_own: torch.Tensor, logits_own: torch.Tensor) -> torch.Tensor:
         """hidden_own bf16 [T/world, H], logits_own f32 [T/world, E] -> bf16 [T/world, H] (this rank's rows
-        of the layer output).  The returned tensor is reused by the next call."""
+        of the layer output).  The returned tensor is reused by the next call.  With a ``guard`` the
+        rank first checks in on the host and raises ``PeerLost`` instead of launching when a rank left
+        or is late (not while the step is being captured into a CUDA graph: replays do not pass here)."""
+        if self.guard is not None:
+            self.guard.check_in()
         if self.peer is not None:
             self.peer.gather_tokens(hidden_own, logits_own)
             if self.fuse_combine:

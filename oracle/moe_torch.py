@@ -53,3 +53,20 @@ def experts(hidden: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, weights,
             y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + 1e-8)
         out.index_add_(0, tok, y * wts[tok, slot].unsqueeze(1))
     return out
+
+
+def shared_expert(hidden: torch.Tensor, shared: dict, rows=None) -> torch.Tensor:
+    """The always-on shared expert (weight 1) on rows ``rows`` (default all), float32 [T,H], other rows
+    zero.  Not in the reference; the same dequantise-then-matmul arithmetic with every token routed
+    to it.  ``shared`` holds w13, w13_sf, w13_gs, w2, w2_sf, w2_gs of the one expert."""
+    x = hidden.float()
+    out = torch.zeros(x.shape, dtype=torch.float32)
+    sel = torch.arange(x.shape[0]) if rows is None else torch.as_tensor(rows, dtype=torch.long)
+    if sel.numel() == 0:
+        return out
+    w13 = dequantize(shared["w13"], shared["w13_sf"], shared["w13_gs"])
+    inter = w13.shape[0] // 2
+    h = x[sel] @ w13.T
+    a = torch.nn.functional.silu(h[:, :inter]) * h[:, inter:]
+    out[sel] = a @ dequantize(shared["w2"], shared["w2_sf"], shared["w2_gs"]).T
+    return out

@@ -16,6 +16,35 @@ from okc_muse_kernels_b200 import ep, synth  # noqa: E402
 from oracle import moe_np  # noqa: E402
 
 
+def wide_rows(rank, world, dev):
+    """A step whose own-row part of the fused combine + reduce has several times more CTAs than the
+    GPU can hold at once (384 own rows x 7 column slices per rank): the kernel must not need them
+    resident together.  Status 0, bit-equal to the unfused exchange, oracle parity on three tokens."""
+    T, H, I, E, K = 384 * world, 7168, 256, 4 * world, 2
+    wl = synth.Workload("wide", T, H, I, E, K)
+    plan = ep.shard_plan(H, I, E, K, world, rank, max_tokens=T)
+    mine = synth.make_weights(wl, seed=23, device=dev, n_experts=plan.local_count, first_expert=plan.local_start)
+    fused = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer")
+    split = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer", fuse_combine=False)
+    t0, t1 = fused.own
+    hidden, logits = synth.make_inputs(wl, seed=123, device=dev)
+    ok = True
+    for _ in range(2):
+        a = fused.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
+        c = split.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
+        for layer in (fused, split):
+            rc, _ = layer.peer.read_status()
+            ok &= rc == 0
+        ok &= bool(torch.equal(a, c))
+    wn = synth.to_numpy_weights(synth.make_weights(wl, seed=23, device=dev))
+    sub = [t0, (t0 + t1) // 2, t1 - 1]
+    _, ref, _, _ = moe_np.moe_step(hidden.cpu().view(torch.uint16).numpy()[sub], logits.cpu().numpy()[sub], wn, K)
+    good, msg = moe_np.compare(a.cpu().view(torch.uint16).numpy()[[s - t0 for s in sub]], ref, 1.5e-2)
+    if not good:
+        print(f"rank {rank} wide rows: {msg}", file=sys.stderr)
+    return ok and good
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -68,6 +97,7 @@ def main():
     ok &= bool(torch.equal(peer.out, want))
     rc, detail = peer.peer.read_status()
     ok &= rc == 0
+    ok &= wide_rows(rank, world, dev)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0 and int(flag.item()) == 1:

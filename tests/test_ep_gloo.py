@@ -84,3 +84,72 @@ def test_shard_plan_and_token_block_errors():
     p = ep.shard_plan(7168, 2048, 256, 8, 8, 3, 128, shared_inter=2048)
     assert (p.local_start, p.local_count) == (96, 32)
     assert ep.token_block(128, 8, 3) == (48, 64)
+
+
+# ------------------------------------------------------------------------------------------------
+# Host-side failure detection (ep.StepGuard): a rank that leaves between steps, and a rank that is
+# late.  Nothing here touches a GPU; the failures are made on the host.
+def _guard_main(rank, world, port, store_port, out_dir, scenario):
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.TCPStore("127.0.0.1", store_port, world, is_master=(rank == 0))
+    guard = ep.StepGuard(store, rank, world, deadline_s=1.5)
+    plan = ep.shard_plan(WL.hidden, WL.inter, 9, 3, world, rank, max_tokens=16)
+    tokens = 6
+
+    def local_step(hidden_all, logits_all, own, out_f32):
+        out_f32.copy_(hidden_all.float() * (rank + 1))
+
+    def cast(src, dst):
+        dst.copy_(src.to(torch.bfloat16))
+
+    layer = ep.ExpertParallelMoE(plan, tokens, group=None, local_step=local_step, cast=cast, guard=guard)
+    t0, t1 = ep.token_block(tokens, world, rank)
+    hidden = torch.ones((tokens, WL.hidden), dtype=torch.bfloat16)
+    logits = torch.zeros((tokens, 9))
+    result = {"rank": rank}
+    out = layer.step(hidden[t0:t1], logits[t0:t1])            # step 0: everybody is there
+    result["step0"] = float(out.float().mean())               # 1 * (1 + 2 + 3)
+    if scenario == "leave" and rank == 2:
+        guard.leave()                                         # between steps, nothing in flight
+        result["left"] = True
+    else:
+        if scenario == "late" and rank == 1:
+            time.sleep(4.0)
+        begin = time.perf_counter()
+        try:
+            layer.step(hidden[t0:t1], logits[t0:t1])
+            result["step1"] = "ran"
+        except ep.PeerLost as exc:
+            result["step1"] = f"PeerLost: {exc}"
+        result["seconds"] = time.perf_counter() - begin
+    import json
+    with open(os.path.join(out_dir, f"r{rank}.json.tmp"), "w") as f:
+        json.dump(result, f)
+    os.replace(os.path.join(out_dir, f"r{rank}.json.tmp"), os.path.join(out_dir, f"r{rank}.json"))
+    if rank == 0:    # rank 0 hosts the store: it stays until every rank has reported
+        t_end = time.monotonic() + 20
+        while time.monotonic() < t_end and not all(os.path.exists(os.path.join(out_dir, f"r{r}.json")) for r in range(world)):
+            time.sleep(0.05)
+    os._exit(0)      # no teardown handshake with ranks that may be gone
+
+
+@pytest.mark.parametrize("scenario", ["leave", "late"])
+def test_a_rank_that_leaves_or_is_late_stops_the_others_on_the_host(scenario, tmp_path):
+    import json
+    world = 3
+    mp.spawn(_guard_main, args=(world, _free_port(), _free_port(), str(tmp_path), scenario), nprocs=world, join=True)
+    res = [json.load(open(tmp_path / f"r{r}.json")) for r in range(world)]
+    assert all(abs(r["step0"] - 6.0) < 1e-6 for r in res)
+    if scenario == "leave":
+        assert res[2].get("left")
+        for r in res[:2]:
+            assert r["step1"].startswith("PeerLost") and "rank 2 left" in r["step1"], r["step1"]
+            assert r["seconds"] < 1.0, "a rank known to have left is noticed without waiting for the deadline"
+    else:
+        for r in (res[0], res[2]):
+            assert r["step1"].startswith("PeerLost") and "within" in r["step1"]
+            assert 1.0 < r["seconds"] < 3.5
+        # the late rank finds that the others gave up on the step and does not launch alone
+        assert res[1]["step1"].startswith("PeerLost") and "gave up on step 1" in res[1]["step1"]

@@ -133,3 +133,23 @@ def test_torch_and_numpy_oracles_agree_on_routing():
     ids_n, w_n = moe_np.route_softmax_topk(logits.numpy(), 8)
     assert np.array_equal(ids_t.numpy(), ids_n)
     assert np.allclose(w_t.numpy(), w_n, rtol=1e-6)
+
+
+def test_torch_and_numpy_oracles_agree_on_the_shared_expert():
+    """The shared expert is not in the reference; both statements of it (the same dequantise-then-matmul
+    arithmetic as a routed expert with weight 1) must agree, on all rows and on a row block."""
+    import torch
+    from okc_muse_kernels_b200 import synth
+    from oracle import moe_torch
+    wl = synth.Workload("sh", 8, 512, 256, 8, 2, shared_inter=256)
+    w = synth.make_weights(wl, seed=3, device="cpu")
+    hidden, _ = synth.make_inputs(wl, seed=4, device="cpu")
+    wn = synth.to_numpy_weights(w)
+    hb = hidden.view(torch.uint16).numpy()
+    for rows in (None, [2, 3, 4]):
+        a = moe_np.shared_expert(hb, {k[7:]: v for k, v in wn.items() if k.startswith("shared_")},
+                                 rows=None if rows is None else np.asarray(rows))
+        b = moe_torch.shared_expert(hidden, {k[7:]: v for k, v in w.items() if k.startswith("shared_")}, rows=rows)
+        assert np.allclose(a, b.numpy(), rtol=1e-5, atol=1e-6)
+        if rows is not None:
+            assert not a[[0, 1, 5, 6, 7]].any() and not b.numpy()[[0, 1, 5, 6, 7]].any()

@@ -53,6 +53,9 @@ def test_static_scratch_step_equals_workspace_step_twice_in_a_row():
         assert torch.equal(ids, ref_ids) and torch.equal(w, ref_w), f"call {call}: routing differs"
         assert torch.equal(got, ref), f"call {call}: output differs from okc_moe_step"
         assert got.float().abs().max() > 0
+        detail = C.c_int32(-1)
+        rc = _lib.lib().okc_moe_read_status_static(torch.cuda.current_stream().cuda_stream, C.byref(detail))
+        assert (rc, detail.value) == (0, 0), "no bounded wait ran out"
 
 
 def test_static_scratch_rejects_plans_that_do_not_fit():
