@@ -246,8 +246,10 @@ int okc_ep_read_status(const okc_ep_comm* comm, okc_stream_t stream, int32_t* de
  * NOT interchangeable: all four are device pointers; any may be NULL).  counts: int32
  * [expert_slots]; sorted: int32 [T*routes_per_token] (route index t*routes_per_token+slot per
  * position, -1 padded); pos: int32 [T*routes_per_token]; items: int32 [1 + 4*max_items]
- * (n_items, then (slot, first position, rows, padded rows) per work item; rows <= 16 when T <= 64 or
- * T * top_k <= 8 * n_experts, else <= 32). */
+ * (n_items, then (slot, first position, rows, padded rows) per work item.  While no expert has more
+ * than 32 rows, experts are cut into items of <= 16 rows when T <= 64 or T * top_k <= 8 * n_experts, else
+ * of <= 32 rows; otherwise an expert with up to 16 rows is one item and every other one is cut into items of
+ * <= 64 rows.  Padded rows are 16, 32 or 64). */
 int okc_moe_export_sort(const okc_moe_plan* plan, const void* workspace, int T, int32_t* counts,
                         int32_t* sorted, int32_t* pos, int32_t* items, int max_items,
                         okc_stream_t stream);

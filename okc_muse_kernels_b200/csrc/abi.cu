@@ -41,8 +41,6 @@ static bool encode_rows_map(CUtensorMap* map, void* base, uint64_t rows, uint64_
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int ncap_for(const okc_moe_plan* plan, int T) { return chunk_rows_for(T, plan->top_k, plan->n_experts); }
-
 static int sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
@@ -244,7 +242,6 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   if (sms <= 0) return OKC_ERR_CUDA;
   Ws w = carve(workspace, g);
   const int R = T * g.kk;
-  const int ncap = ncap_for(plan, T);
 
   if (ev && cudaEventRecord(ev[0], stream) != cudaSuccess) return OKC_ERR_CUDA;
   if (launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, w.done, g.max_items, stream) != cudaSuccess)
@@ -255,8 +252,8 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   // unit waiting for the gate_up units of its own work item only.
   MoeGemmParams a;
   memset(&a, 0, sizeof(a));
-  const uint32_t boxes[2] = {16, 32};
-  for (int i = 0; i < 2; ++i) {
+  const uint32_t boxes[3] = {16, 32, 64};
+  for (int i = 0; i < 3; ++i) {
     if (!encode_rows_map(&a.ph[0].bmap[i], w.xg, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.H), boxes[i])) return OKC_ERR_CUDA;
     if (!encode_rows_map(&a.ph[1].bmap[i], w.inter, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.I), boxes[i])) return OKC_ERR_CUDA;
   }
@@ -265,7 +262,6 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   a.ph[1].wpacked = static_cast<const uint8_t*>(packed_w2); a.ph[1].gs = gs2;
   a.ph[1].pairs = g.pairs2; a.ph[1].stages = g.stages2; a.ph[1].expert_bytes = g.w2_expert_bytes;
   a.meta = w.meta; a.items = w.items; a.done = w.done;
-  a.ncap = ncap; a.n_stages = gemm_stages_for(ncap);
   a.inter = w.inter; a.I = g.I; a.H = g.H; a.y = w.y; a.sorted = w.sorted; a.wsorted = w.wsorted;
   a.weighted = plan->post_norm ? 0 : 1;
   a.phase_lo = 0; a.phase_hi = 1; a.work_counter = w.meta + kMetaWorkFused;

@@ -17,13 +17,40 @@ constexpr int kTileCodeBytes = kChunks * kTileRows * 16;   // 16384
 constexpr int kTileScaleBytes = kChunks * kTileRows * 2;   // 2048
 constexpr int kTileBytes = kTileCodeBytes + kTileScaleBytes;
 constexpr int kStageBytes = 2 * kTileBytes;    // 36864: two tiles (gate+up, or two row tiles of w2)
-constexpr int kChunkRows = 32;                 // most rows (tokens) of one work item
-// Rows per work item for a step of T tokens, k routes each, over E experts: 16 while the step is
-// decode-sized or an expert gets 8 rows or fewer on average (the accumulators of eight issuers then
-// fit TMEM twice, so the epilogue overlaps the next unit, and the stage ring is a stage deeper);
-// 32 beyond, where 16-row items would stream and dequantise most experts' weights twice.
+constexpr int kNarrowRows = 32;                // most rows (tokens) of a narrow work item
+constexpr int kChunkRows = 64;                 // most rows of any work item (a wide one)
+// Work items.  While no expert of the step has more than 32 rows, every expert becomes narrow items of
+// at most chunk_rows_for() rows: 16 while the step is decode-sized or an expert gets 8 rows or fewer on
+// average (the accumulators of eight issuers then fit TMEM twice, so the epilogue overlaps the next
+// unit, and the stage ring is a stage deeper); 32 beyond, where 16-row items would stream and
+// dequantise most experts' weights twice.
+// A step in which some expert has more than 32 rows is a wide step: an expert is cut into items of 64
+// rows, what is left over at its end being one more item; items of up to 16 rows are narrow ones, all
+// others wide ones padded to 32 or 64 rows (one accumulator per tile: two wide items' accumulators, or
+// two 16-row items' partial sums, fit TMEM side by side, so the epilogue always overlaps the next unit).
 __host__ __device__ inline int chunk_rows_for(int T, int k, int E) {
-  return (T <= 64 || static_cast<long long>(T) * k <= 8LL * E) ? 16 : kChunkRows;
+  return (T <= 64 || static_cast<long long>(T) * k <= 8LL * E) ? 16 : kNarrowRows;
+}
+__host__ __device__ inline int item_pad(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
+// rows per item of an expert with c rows; cmax = rows of the step's heaviest expert, chunk = chunk_rows_for()
+__host__ __device__ inline int item_rows(int c, int cmax, int chunk) {
+  if (cmax <= kNarrowRows) return chunk;
+  return c <= 16 ? 16 : kChunkRows;
+}
+
+// Shared memory of the grouped-GEMM kernel: a reserve for its control block and the 1024-byte alignment
+// of the ring, then as many ring slots as fit 227 KB.  wcap = rows of the widest item of the step.
+// Up to 32 rows a slot is a whole stage (the 36 KB weight image + wcap token rows of 256 K elements);
+// beyond, half a stage (18 KB of weights + wcap token rows of 128 K elements).
+constexpr int kSmemBudget = 232448;
+constexpr int kGemmCtrlReserve = 2048;
+constexpr int kMaxStages = 6;
+__host__ __device__ inline int gemm_slot_bytes(int wcap) {
+  return wcap > kNarrowRows ? 36864 / 2 + wcap * 256 : 36864 + wcap * 512;
+}
+__host__ __device__ inline int gemm_slots_for(int wcap) {
+  const int n = (kSmemBudget - kGemmCtrlReserve - 1024) / gemm_slot_bytes(wcap);
+  return n > kMaxStages ? kMaxStages : n;
 }
 constexpr int kMaxSlots = 513;                 // 512 experts + shared
 constexpr int kMaxRoutes = 16384;              // routes (tokens x routes per token) one step may hold
@@ -33,6 +60,7 @@ constexpr uint32_t kLeftMask = 0x60306030u;    // bits of w0 its three rotations
 
 // meta words at the start of the workspace
 enum MetaWord { kMetaItems = 0, kMetaLocalRoutes = 1, kMetaStatus = 2, kMetaDetail = 3, kMetaTokens = 4,
+                kMetaWcap = 5,       // rows of the step's widest work item, padded: 16, 32 or 64 (64: a wide step)
                 kMetaWorkFused = 8, kMetaWorkPhase0 = 9, kMetaWorkPhase1 = 10,   // unit counters of the GEMM launches
                 kMetaWords = 64 };
 

@@ -11,22 +11,31 @@
 //                 token operand (128-byte swizzle) per stage, mbarrier ring
 //   warps 0..7    MMA issuers, one thread each.  A thread needs 100+ cycles to issue one
 //                 tcgen05.mma whatever its N (more when its warp competes for issue slots), and
-//                 issue from several warps overlaps, so the 32 MMAs of a stage are spread over
-//                 eight issuers: (tile of the pair) x (64-wide K block of the stage).  Each issuer
-//                 adds into its own accumulator, which keeps the order of additions fixed; the
-//                 epilogue adds the four K-block partials in a fixed order.  Warp 0 owns the TMEM
-//                 allocation
+//                 issue from several warps overlaps, so the 32 MMAs of a narrow item's stage are
+//                 spread over eight issuers: (tile of the pair) x (64-wide K block of the stage).
+//                 Each issuer adds into its own accumulator, which keeps the order of additions
+//                 fixed; the epilogue adds the four K-block partials in a fixed order.  For a wide
+//                 item the two issuers of K block 0 issue all MMAs of their tile in K order, the
+//                 others only keep the barriers' books.  Warp 0 owns the TMEM allocation
 //   warps 8..23   dequantisers in two groups of 8 that take alternate A slots: thread = one weight
 //                 row of one tile; FP4 + E4M3 from shared memory -> bf16x2 registers -> tcgen05.st
 //                 into the 4-slot ring of A operands in TMEM (slot = one 64-wide K block)
 //   warps 24..27  epilogue: tcgen05.ld of the accumulators (sum of the partials), scale,
 //                 activation, store
 //
+// Work items are "narrow" (N = 16 or 32: the K blocks of a stage spread over eight issuers with a
+// partial accumulator each) or, in a step where some expert has more than 32 rows, "wide" (N = 32 or
+// 64, one issuer and one accumulator per tile, so that an expert with hundreds of rows is streamed
+// and dequantised once per 64 rows).  The geometry of a launch (ring slot size and depth, accumulator
+// buffers) follows the widest item of the step, which the sort kernel leaves in the workspace.
+//
 // The reference computes the same products with mma.sync / wgmma on Hopper
 // (muse_moe_w4a16/submission.py:3828-4014 `tk2f_consume`, :1909-2072 `tw_item`); nothing is shared
 // with that code beyond the arithmetic (weights as the M operand, FP32 accumulation, the
 // global scale and a power of two applied once in the epilogue, submission.py:3855,3983-3987).
 #include <cuda_bf16.h>
+
+#include <type_traits>
 
 #include "params.cuh"
 
@@ -41,8 +50,8 @@ constexpr int kProducerWarp = 28;
 constexpr int kASlots = 4;            // ring of A operands in TMEM, 64 columns each (K = 64, two tiles)
 constexpr int kASlotCols = 64;
 constexpr int kAccCol0 = 256;         // accumulators live in TMEM columns [256, 512)
+constexpr int kWideAccCols = 64;      // a wide item's accumulator: one block of 64 columns per tile
 constexpr int kTmemCols = 512;
-constexpr int kMaxStages = 6;
 
 // Codes written to the status word when a wait gives up: role * 16 + barrier kind.
 enum WaitCode { kWaitProducerEmpty = 0x11, kWaitProducerUnit = 0x12, kWaitProducerDone = 0x13,
@@ -115,10 +124,12 @@ __device__ __forceinline__ bool next_unit(Ctrl* ctrl, uint32_t bar_ufull, uint32
 
 __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_constant__ MoeGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
+  // the ring first, 1024-byte aligned; the control block behind the largest ring any step can ask for,
+  // so that its place does not depend on the step (with the barriers in front of the ring the kernel
+  // was measured 3 % slower)
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem0 - smem_u32(smem_raw));
-  const uint32_t stage_bytes = kStageBytes + static_cast<uint32_t>(p.ncap) * 512u;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_gen + static_cast<size_t>(p.n_stages) * stage_bytes);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_gen + (kSmemBudget - kGemmCtrlReserve - 1024));
   volatile int* abort_flag = &ctrl->abort_code;
 
   const int tid = threadIdx.x, lane = tid & 31;
@@ -126,11 +137,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
   // what is derived from it (roles, barrier addresses, TMEM columns) in uniform registers
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const bool lane0 = lane == 0;
-  const int NS = p.n_stages;
-  // accumulators in TMEM columns [256, 512): per buffer eight blocks of ncap columns,
-  // block (tile * 4 + K block of the stage); ncap is 16 (two buffers) or 32 (one)
-  const int nbuf = (p.ncap <= 16) ? 2 : 1;
-  const uint32_t acc_buf_stride = 8u * p.ncap;
   // shared-memory addresses of the barrier arrays (element i is 8 bytes further)
   const uint32_t bar_full = smem_u32(&ctrl->full[0]), bar_empty = smem_u32(&ctrl->empty[0]);
   const uint32_t bar_afull = smem_u32(&ctrl->a_full[0]), bar_aempty = smem_u32(&ctrl->a_empty[0]);
@@ -138,7 +144,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
   const uint32_t bar_ufull = smem_u32(&ctrl->u_full[0]), bar_uempty = smem_u32(&ctrl->u_empty[0]);
 
   if (tid == 0) {
-    for (int i = 0; i < NS; ++i) {
+    for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_empty + 8 * i, kDequantWarps + kIssuers);
     }
@@ -172,11 +178,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
   griddep_wait();
   griddep_launch_dependents();
 
+  // Geometry of this launch from the widest item of the step (16, 32, 64 or 128 rows; written by the
+  // sort kernel): a stage holds the 36 KB weight image and wcap token rows of 256 K elements.
+  // (through a shuffle, like the warp index: what is derived from it then lives in uniform registers and
+  // costs the dequantisers' loop no integer-pipe instructions)
+  const int wcap = __shfl_sync(0xffffffffu, min(max(p.meta[kMetaWcap], 16), kChunkRows), 0);
+  // A ring slot holds a whole stage (256 K elements: the 36 KB weight image + wcap token rows) while
+  // every item is narrow.  A step with wide items runs on half stages (128 K elements: half of each
+  // tile's codes and scales + wcap token rows of 128 elements): six slots instead of three, so that
+  // more copies are in flight while a slot is being consumed.
+  const bool half = wcap > kNarrowRows;
+  const int sps = half ? 2 : 1;                                  // ring slots per stage
+  const uint32_t slot_bytes = gemm_slot_bytes(wcap);
+  const int NS = gemm_slots_for(wcap);
+  // Accumulators in TMEM columns [256, 512).  Narrow items: per buffer eight blocks of acols columns,
+  // block (tile * 4 + K block of the stage).  Wide items: per buffer one block of 64 columns per tile.
+  // Two buffers of 128 columns, except in a step of narrow items of up to 32 rows (one of 256).
+  const int nbuf = (wcap == kNarrowRows) ? 1 : 2;
+  const int acols = (wcap == kNarrowRows) ? 32 : 16;
+  const uint32_t acc_buf_stride = 8u * acols;
+
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       for (int ph = 0; ph < 2; ++ph)
-        for (int i = 0; i < 2; ++i) tma_prefetch_desc(&p.ph[ph].bmap[i]);
+        for (int i = 0; i < 3; ++i) tma_prefetch_desc(&p.ph[ph].bmap[i]);
       const uint64_t pol = policy_evict_first();
       const int n_items = p.meta[kMetaItems];
       const int units0 = n_items * p.ph[0].pairs, units1 = n_items * p.ph[1].pairs;
@@ -207,25 +233,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
         u.slot = wi.x; u.pos0 = wi.y; u.rows = wi.z; u.npad = wi.w; u.stages = pp.stages;
         ctrl->units[k] = u;
         mbar_arrive(bar_ufull + 8 * k);
-        const int mi = (u.npad == 16) ? 0 : 1;
+        const int mi = (u.npad == 16) ? 0 : (u.npad == 32) ? 1 : 2;
         const uint8_t* src = pp.wpacked + static_cast<size_t>(u.slot) * pp.expert_bytes +
                              static_cast<size_t>(u.pair) * pp.stages * kStageBytes;
-        int s_begin = 0;
+        const int steps = pp.stages * sps;                       // ring slots this unit goes through
+        const uint32_t tx_bytes = half ? kStageBytes / 2 + u.npad * 256 : kStageBytes + u.npad * 512;
+        // weights of ring step r of the unit -> slot at dst
+        auto send_weights = [&](int r, uint32_t dst, uint32_t bar) {
+          if (!half) {
+            bulk_g2s_hint(dst, src + static_cast<size_t>(r) * kStageBytes, kStageBytes, bar, pol);
+          } else {
+            const uint8_t* sp = src + static_cast<size_t>(r >> 1) * kStageBytes;
+            const int hh = r & 1;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              bulk_g2s_hint(dst + t * (kTileBytes / 2), sp + t * kTileBytes + hh * (kTileCodeBytes / 2), kTileCodeBytes / 2, bar, pol);
+              bulk_g2s_hint(dst + t * (kTileBytes / 2) + kTileCodeBytes / 2,
+                            sp + t * kTileBytes + kTileCodeBytes + hh * (kTileScaleBytes / 2), kTileScaleBytes / 2, bar, pol);
+            }
+          }
+        };
+        // token rows of ring step r -> behind the weights of the slot
+        auto send_tokens = [&](int r, uint32_t dst, uint32_t bar) {
+          if (!half) {
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb)
+              tma_2d_g2s(dst + kStageBytes + kb * u.npad * 128, &pp.bmap[mi], r * kStageK + kb * 64, u.pos0, bar);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_2d_g2s(dst + kStageBytes / 2 + j * u.npad * 128, &pp.bmap[mi], (r >> 1) * kStageK + ((r & 1) * 2 + j) * 64, u.pos0, bar);
+          }
+        };
+        int r_begin = 0;
         if (u.phase == 1) {
           // The token operand of a down unit is the gate_up output of its work item: all four
           // epilogue warps of each of the item's gate_up units must have stored and published it.
           const int target = 4 * p.ph[0].pairs;
           if (ld_acquire_gpu(p.done + u.item) < target) {
-            // Not yet.  The weights do not depend on it: start their copies for as many stages as the
-            // ring holds, wait, then send the token tiles after them (a stage's barrier completes
+            // Not yet.  The weights do not depend on it: start their copies for as many slots as the
+            // ring holds, wait, then send the token tiles after them (a slot's barrier completes
             // when both parts have arrived).
-            const int pre = pp.stages < NS ? pp.stages : NS;
+            const int pre = steps < NS ? steps : NS;
             int st2 = st, sent = 0;
             uint32_t ph2 = ph;
-            for (int s = 0; s < pre; ++s) {
+            for (int r = 0; r < pre; ++r) {
               if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st2, ph2 ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
-              mbar_expect_tx(bar_full + 8 * st2, kStageBytes + u.npad * 512);
-              bulk_g2s_hint(smem0 + st2 * stage_bytes, src + static_cast<size_t>(s) * kStageBytes, kStageBytes, bar_full + 8 * st2, pol);
+              mbar_expect_tx(bar_full + 8 * st2, tx_bytes);
+              send_weights(r, smem0 + st2 * slot_bytes, bar_full + 8 * st2);
               ++sent;
               if (++st2 == NS) { st2 = 0; ph2 ^= 1; }
             }
@@ -238,31 +293,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
               }
             }
             fence_proxy_async();   // those stores were generic-proxy writes; the loads below are TMA
-            // (also when giving up: the stages whose weights are in flight get their token tiles, so
+            // (also when giving up: the slots whose weights are in flight get their token tiles, so
             // that their barriers complete and the CTA can wait for its copies before it retires)
-            for (int s = 0; s < sent; ++s) {
-              const uint32_t dst = smem0 + st * stage_bytes;
-#pragma unroll
-              for (int kb = 0; kb < 4; ++kb)
-                tma_2d_g2s(dst + kStageBytes + kb * u.npad * 128, &pp.bmap[mi], s * kStageK + kb * 64, u.pos0, bar_full + 8 * st);
+            for (int r = 0; r < sent; ++r) {
+              send_tokens(r, smem0 + st * slot_bytes, bar_full + 8 * st);
               ++issued;
               if (++st == NS) { st = 0; ph ^= 1; }
             }
             if (!ok) break;
-            s_begin = pre;
+            r_begin = pre;
           } else {
             fence_proxy_async();
           }
         }
-        for (int s = s_begin; s < pp.stages; ++s) {
+        for (int r = r_begin; r < steps; ++r) {
           if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
           const uint32_t bar = bar_full + 8 * st;
-          const uint32_t dst = smem0 + st * stage_bytes;
-          mbar_expect_tx(bar, kStageBytes + u.npad * 512);
-          bulk_g2s_hint(dst, src + static_cast<size_t>(s) * kStageBytes, kStageBytes, bar, pol);
-#pragma unroll
-          for (int kb = 0; kb < 4; ++kb)
-            tma_2d_g2s(dst + kStageBytes + kb * u.npad * 128, &pp.bmap[mi], s * kStageK + kb * 64, u.pos0, bar);
+          const uint32_t dst = smem0 + st * slot_bytes;
+          mbar_expect_tx(bar, tx_bytes);
+          send_weights(r, dst, bar);
+          send_tokens(r, dst, bar);
           ++issued;
           if (++st == NS) { st = 0; ph ^= 1; }
         }
@@ -281,52 +331,138 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
     }
   } else if (warp < kIssuers) {
     // ------------------------------------------------------------ MMA issuers
-    if (lane == 0) {
-      const int tile = warp & 1, kb = warp >> 1;
-      const uint32_t my_afull = bar_afull + 16 * kb + 8 * tile, my_aempty = bar_aempty + 16 * kb + 8 * tile;
-      const uint32_t a0 = tmem + kb * kASlotCols + tile * 32;
-      int st = 0;
-      uint32_t ph = 0, sph = 0;     // stage ring phase; A-slot phase (flips once per stage)
-      OKC_PROF_DECL
-      const uint32_t desc_hi = static_cast<uint32_t>(smem_desc_sw128(0) >> 32);
-      const uint32_t desc_lo_const = static_cast<uint32_t>(smem_desc_sw128(0));
-      UnitDesc u;
-      for (uint32_t unit_it = 0; next_unit<false>(ctrl, bar_ufull, bar_uempty, unit_it, true, abort_flag, kWaitMmaUnit, u); ++unit_it) {
-        const uint32_t npad = static_cast<uint32_t>(u.npad);
-        const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
-        if (!OKC_PROF_WAIT(2, mbar_wait<500>(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) goto issuer_done;
-        tc_fence_after();
-        const uint32_t idesc = idesc_bf16_m128(npad);
-        const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + (tile * 4 + kb) * p.ncap;
-        const uint32_t kb_off = kb * ((npad * 128u) >> 4);   // descriptor units to this issuer's K block
-        uint32_t acc = 0;
-        for (int s = 0; s < u.stages; ++s) {
-          if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) goto issuer_done;
-          const uint32_t lo = (desc_lo_const | (((smem0 + st * stage_bytes + kStageBytes) & 0x3FFFFu) >> 4)) + kb_off;
-          if (!OKC_PROF_WAIT(4, mbar_wait(my_afull, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
+    // The whole warp runs the loops and the waits (a poll costs one warp instruction however many lanes
+    // take part); one elected lane issues the MMAs and their commits.  Control flow that is the same in
+    // all lanes lets the compiler keep descriptors, barrier addresses and counters in uniform registers,
+    // where tcgen05.mma takes them from: from a single-lane branch every operand of every MMA has to be
+    // moved there first.
+    {
+      // (a generic lambda with a compile-time flag: the loops of the whole-stage ring stay as lean as
+      // they were before half stages existed)
+      auto issue = [&](auto half_tag) {
+        constexpr bool kHalf = decltype(half_tag)::value;
+        const int tile = warp & 1, kb = warp >> 1;
+        const uint32_t my_afull = bar_afull + 16 * kb + 8 * tile, my_aempty = bar_aempty + 16 * kb + 8 * tile;
+        const uint32_t a0 = tmem + kb * kASlotCols + tile * 32;
+        const uint32_t b_off = kHalf ? kStageBytes / 2 : kStageBytes;    // token rows behind the weights of a slot
+        int st = 0;
+        uint32_t ph = 0, sph = 0;     // ring phase; A-slot phase (flips once per stage)
+        OKC_PROF_DECL
+        const uint32_t desc_hi = static_cast<uint32_t>(smem_desc_sw128(0) >> 32);
+        const uint32_t desc_lo_const = static_cast<uint32_t>(smem_desc_sw128(0));
+        UnitDesc u;
+        for (uint32_t unit_it = 0; next_unit<true>(ctrl, bar_ufull, bar_uempty, unit_it, lane0, abort_flag, kWaitMmaUnit, u); ++unit_it) {
+          const uint32_t npad = static_cast<uint32_t>(u.npad);
+          const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
+          if (!OKC_PROF_WAIT(2, mbar_wait<500>(bar_accempty + 8 * buf, ((unit_it / nbuf) & 1) ^ 1, abort_flag, kWaitMmaAccEmpty))) goto issuer_done;
           tc_fence_after();
-          mma_ts2(d, a0, lo, desc_hi, idesc, acc);
-          mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
-          mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
-          mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
-          acc = 1;
-          mma_commit(my_aempty);
-          mma_commit(bar_empty + 8 * st);
-          sph ^= 1;
-          if (++st == NS) { st = 0; ph ^= 1; }
+          const uint32_t idesc = idesc_bf16_m128(npad);
+          const uint32_t kb_step = (npad * 128u) >> 4;           // descriptor units from one K block's rows to the next
+          if (!kHalf || npad <= 16) {
+            // narrow item: this issuer's K block of every stage into its own partial accumulator
+            const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + (tile * 4 + kb) * acols;
+            uint32_t acc = 0;
+            for (int s = 0; s < u.stages; ++s) {
+#pragma unroll
+              for (int hh = 0; hh < (kHalf ? 2 : 1); ++hh) {
+                if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) goto issuer_done;
+                if (!kHalf || hh == (kb >> 1)) {
+                  const uint32_t lo = (desc_lo_const | (((smem0 + st * slot_bytes + b_off) & 0x3FFFFu) >> 4)) +
+                                      (kHalf ? (kb & 1) : kb) * kb_step;
+                  if (!OKC_PROF_WAIT(4, mbar_wait(my_afull, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
+                  tc_fence_after();
+                  if (elect_one()) {
+                    mma_ts2(d, a0, lo, desc_hi, idesc, acc);
+                    mma_ts2(d, a0 + 8, lo + 2, desc_hi, idesc, 1);
+                    mma_ts2(d, a0 + 16, lo + 4, desc_hi, idesc, 1);
+                    mma_ts2(d, a0 + 24, lo + 6, desc_hi, idesc, 1);
+                    mma_commit(my_aempty);
+                    mma_commit(bar_empty + 8 * st);
+                  }
+                  __syncwarp();
+                  acc = 1;
+                } else {
+                  mbar_arrive_if(bar_empty + 8 * st, lane0);     // the other half of the stage: not this issuer's K block
+                }
+                if (++st == NS) { st = 0; ph ^= 1; }
+              }
+              if (kHalf && kb == 0) {
+                // In a wide step this thread issues for all four A slots of its tile whenever the unit is a
+                // wide one.  A parity wait only tells phases one apart, so it keeps step with the other
+                // three slots in narrow units too: it sees every phase of their barriers complete.
+#pragma unroll
+                for (int k4 = 1; k4 < kASlots; ++k4)
+                  if (!OKC_PROF_WAIT(4, mbar_wait<200>(bar_afull + 16 * k4 + 8 * tile, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
+              }
+              sph ^= 1;
+            }
+            if (elect_one()) mma_commit(bar_accfull + 8 * buf);
+            __syncwarp();
+          } else if (kb == 0) {
+            // wide item: all K blocks of this tile, in K order, into the tile's one accumulator
+            const uint32_t d = tmem + kAccCol0 + buf * acc_buf_stride + tile * kWideAccCols;
+            const uint32_t a_tile = tmem + tile * 32;
+            uint32_t acc = 0;
+            for (int s = 0; s < u.stages; ++s) {
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                if (!OKC_PROF_WAIT(3, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) goto issuer_done;
+                uint32_t lo = desc_lo_const | (((smem0 + st * slot_bytes + b_off) & 0x3FFFFu) >> 4);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  const int k4 = 2 * hh + j;
+                  if (!OKC_PROF_WAIT(4, mbar_wait(bar_afull + 16 * k4 + 8 * tile, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
+                  tc_fence_after();
+                  const uint32_t a = a_tile + k4 * kASlotCols;
+                  if (elect_one()) {
+                    mma_ts2(d, a, lo, desc_hi, idesc, acc);
+                    mma_ts2(d, a + 8, lo + 2, desc_hi, idesc, 1);
+                    mma_ts2(d, a + 16, lo + 4, desc_hi, idesc, 1);
+                    mma_ts2(d, a + 24, lo + 6, desc_hi, idesc, 1);
+                    mma_commit(bar_aempty + 16 * k4 + 8 * tile);
+                    if (j == 1) mma_commit(bar_empty + 8 * st);
+                  }
+                  __syncwarp();
+                  acc = 1;
+                  lo += kb_step;
+                }
+                if (++st == NS) { st = 0; ph ^= 1; }
+              }
+              sph ^= 1;
+            }
+            if (elect_one()) mma_commit(bar_accfull + 8 * buf);
+            __syncwarp();
+          } else {
+            // wide item, an issuer without MMAs of its own: keeps the ring's and the accumulator's barrier
+            // counts.  It also waits for its A slot of every stage as if it had MMAs to issue: a parity
+            // wait only tells phases one apart, so a thread that will wait on that barrier again in the
+            // next narrow unit must never run more than one stage ahead of it.
+            for (int s = 0; s < u.stages; ++s) {
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                if (!OKC_PROF_WAIT(3, mbar_wait<200>(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) goto issuer_done;
+                if (hh == (kb >> 1) && !OKC_PROF_WAIT(4, mbar_wait<200>(my_afull, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
+                mbar_arrive_if(bar_empty + 8 * st, lane0);
+                if (++st == NS) { st = 0; ph ^= 1; }
+              }
+              sph ^= 1;
+            }
+            mbar_arrive_if(bar_accfull + 8 * buf, lane0);
+          }
         }
-        mma_commit(bar_accfull + 8 * buf);
-      }
-    issuer_done:
-      if (*abort_flag != 0) {
-        // giving up: the MMAs already issued still read the A ring and write the accumulators, so
-        // tensor memory may only be freed once they have retired (bounded, like the producer's drain)
-        const uint32_t bar = smem_u32(&ctrl->drain[warp]);
-        mma_commit(bar);
-        const long long t0 = clock64();
-        while (!mbar_try(bar, 0) && clock64() - t0 < kWaitLimitCycles) {}
-      }
-      if (warp == 0) { OKC_PROF_STORE(5, 2, 5) }
+      issuer_done:
+        if (*abort_flag != 0 && lane0) {
+          // giving up: the MMAs already issued still read the A ring and write the accumulators, so
+          // tensor memory may only be freed once they have retired (bounded, like the producer's drain)
+          const uint32_t bar = smem_u32(&ctrl->drain[warp]);
+          mma_commit(bar);
+          const long long t0 = clock64();
+          while (!mbar_try(bar, 0) && clock64() - t0 < kWaitLimitCycles) {}
+        }
+        if (warp == 0 && lane0) { OKC_PROF_STORE(5, 2, 5) }
+      };
+      if (half) issue(std::true_type{});
+      else issue(std::false_type{});
     }
   } else if (warp >= kDequantWarp0 && warp < kDequantWarp0 + kDequantWarps) {
     // ------------------------------------------------------------ dequantisers
@@ -338,76 +474,90 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
     const int grp = dw >> 3;
     const int row = q * 32 + lane;
     const uint32_t trow = tmem + (static_cast<uint32_t>(q * 32) << 16) + tile * 32;
-    const uint32_t code_off = tile * kTileBytes + row * 16;
-    const uint32_t scale_off = tile * kTileBytes + kTileCodeBytes + row * 2;
-    const uint32_t my_afull = bar_afull + 8 * tile, my_aempty = bar_aempty + 8 * tile;
-    int st = 0;
-    // barrier of the A slot stored to but not yet handed over; a barrier nobody waits on stands in
-    // before the first slot, so the hand-over below needs no "is anything pending" test
-    uint32_t pend_bar = smem_u32(&ctrl->dummy);
-    uint32_t ph = 0, sph = 0;
-    OKC_PROF_DECL
-    UnitDesc u;
-    for (uint32_t unit_it = 0; next_unit<true>(ctrl, bar_ufull, bar_uempty, unit_it, lane0, abort_flag, kWaitDqUnit, u); ++unit_it) {
-      for (int s = 0; s < u.stages; ++s) {
-        if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) goto dq_done;
-        {
-          const uint8_t* img = smem_gen + static_cast<size_t>(st) * stage_bytes;
-          const uint32_t simg = smem0 + st * stage_bytes + scale_off;
+    auto dequantise = [&](auto half_tag) {
+      constexpr bool kHalf = decltype(half_tag)::value;
+      // a tile's part of a ring slot: codes [chunks][128 rows][16 B], then scales [chunks][128 rows][2 B];
+      // eight chunks (a whole stage) or four (half a stage)
+      constexpr uint32_t kSlotTile = kHalf ? kTileBytes / 2 : kTileBytes;
+      constexpr uint32_t kSlotCodes = kHalf ? kTileCodeBytes / 2 : kTileCodeBytes;
+      const uint32_t code_off = tile * kSlotTile + row * 16;
+      const uint32_t scale_off = tile * kSlotTile + kSlotCodes + row * 2;
+      const uint32_t my_afull = bar_afull + 8 * tile, my_aempty = bar_aempty + 8 * tile;
+      int st = 0;
+      // barrier of the A slot stored to but not yet handed over; a barrier nobody waits on stands in
+      // before the first slot, so the hand-over below needs no "is anything pending" test
+      uint32_t pend_bar = smem_u32(&ctrl->dummy);
+      uint32_t ph = 0, sph = 0;
+      OKC_PROF_DECL
+      UnitDesc u;
+      for (uint32_t unit_it = 0; next_unit<true>(ctrl, bar_ufull, bar_uempty, unit_it, lane0, abort_flag, kWaitDqUnit, u); ++unit_it) {
+        for (int s = 0; s < u.stages; ++s) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int kb = grp + 2 * h;
-            // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
-            const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb) * (kTileRows * 16));
-            const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (2 * kb + 1) * (kTileRows * 16));
-            const uint32_t sp0 = simg + (2 * kb) * (kTileRows * 2);
-            const uint32_t sp1 = sp0 + kTileRows * 2;
-            const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
-            uint32_t r[16];
-            dequant_chunk(w0, s00, s01, r);
-            // the stores of the previous slot completed while this chunk was being dequantised:
-            // only now wait for them and hand that slot to its MMA issuer
-            OKC_PROF_VOID(8, tmem_wait_st())
-            tc_fence_before();
-            mbar_arrive_if(pend_bar, lane0);
-            // every lane polls the same barrier in the same instruction, so the outcome is the same
-            // in all of them and the warp stays converged for the tensor-memory stores below
-            if (!OKC_PROF_WAIT(7, mbar_wait(my_aempty + 16 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) goto dq_done;
-            tc_fence_after();
-            tmem_st16(trow + kb * kASlotCols, r);
-            dequant_chunk(w1, s10, s11, r);
-            tmem_st16(trow + kb * kASlotCols + 16, r);
-            pend_bar = my_afull + 16 * kb;
+          for (int hh = 0; hh < (kHalf ? 2 : 1); ++hh) {
+            if (!OKC_PROF_WAIT(6, mbar_wait(bar_full + 8 * st, ph, abort_flag, kWaitDqFull))) goto dq_done;
+            {
+              const uint8_t* img = smem_gen + static_cast<size_t>(st) * slot_bytes;
+              const uint32_t simg = smem0 + st * slot_bytes + scale_off;
+#pragma unroll
+              for (int h = 0; h < (kHalf ? 1 : 2); ++h) {
+                // whole stages: this group's two K blocks of the stage; half stages: its K block of this half
+                const int kb = kHalf ? 2 * hh + grp : grp + 2 * h;
+                const int c0 = kHalf ? 2 * grp : 2 * kb;         // first of the slot's two chunks within the ring slot
+                // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
+                const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + c0 * (kTileRows * 16));
+                const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (c0 + 1) * (kTileRows * 16));
+                const uint32_t sp0 = simg + c0 * (kTileRows * 2);
+                const uint32_t sp1 = sp0 + kTileRows * 2;
+                const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
+                uint32_t r[16];
+                dequant_chunk(w0, s00, s01, r);
+                // the stores of the previous slot completed while this chunk was being dequantised:
+                // only now wait for them and hand that slot to its MMA issuer
+                OKC_PROF_VOID(8, tmem_wait_st())
+                tc_fence_before();
+                mbar_arrive_if(pend_bar, lane0);
+                // every lane polls the same barrier in the same instruction, so the outcome is the same
+                // in all of them and the warp stays converged for the tensor-memory stores below
+                if (!OKC_PROF_WAIT(7, mbar_wait(my_aempty + 16 * kb, sph ^ 1, abort_flag, kWaitDqAEmpty))) goto dq_done;
+                tc_fence_after();
+                tmem_st16(trow + kb * kASlotCols, r);
+                dequant_chunk(w1, s10, s11, r);
+                tmem_st16(trow + kb * kASlotCols + 16, r);
+                pend_bar = my_afull + 16 * kb;
+              }
+            }
+            // the slot's bytes have been consumed (the loads fed the arithmetic above): hand the
+            // shared-memory slot back
+            mbar_arrive_if(bar_empty + 8 * st, lane0);
+            if (++st == NS) { st = 0; ph ^= 1; }
           }
+          sph ^= 1;
         }
-        // the stage's bytes have been consumed (the loads fed the arithmetic above): hand the
-        // shared-memory slot back
-        mbar_arrive_if(bar_empty + 8 * st, lane0);
-        sph ^= 1;
-        if (++st == NS) { st = 0; ph ^= 1; }
+        // The unit's last slot is normally handed over while the first chunk of the next unit is
+        // being dequantised.  If that chunk has not arrived, hand the slot over now: the producer may
+        // be holding the next unit back until another CTA's -- or this CTA's -- gate_up epilogue has
+        // run, and this unit's epilogue cannot run before its last MMAs have their operand.
+        if (!__all_sync(0xffffffffu, mbar_test(bar_full + 8 * st, ph))) {
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive_if(pend_bar, lane0);
+          pend_bar = smem_u32(&ctrl->dummy);
+        }
       }
-      // The unit's last slot is normally handed over while the first chunk of the next unit is
-      // being dequantised.  If that chunk has not arrived, hand the slot over now: the producer may
-      // be holding the next unit back until another CTA's -- or this CTA's -- gate_up epilogue has
-      // run, and this unit's epilogue cannot run before its last MMAs have their operand.
-      if (!__all_sync(0xffffffffu, mbar_test(bar_full + 8 * st, ph))) {
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive_if(pend_bar, lane0);
-        pend_bar = smem_u32(&ctrl->dummy);
-      }
-    }
-  dq_done:
-    tmem_wait_st();
-    tc_fence_before();
-    mbar_arrive_if(pend_bar, lane0);
+    dq_done:
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_if(pend_bar, lane0);
 #ifdef OKC_WAIT_PROFILE
-    if (lane == 0 && blockIdx.x < kProfCtas && (warp == kDequantWarp0 || warp == kDequantWarp0 + kDequantWarps - 1)) {
-      const int base = (warp == kDequantWarp0) ? 6 : 10;   // first and last dequantiser warp
-      for (int i = 0; i < 3; ++i) g_wait_prof[blockIdx.x][base + i] = prof_acc[6 + i];
-      g_wait_prof[blockIdx.x][base + 3] = clock64() - prof_t0;
-    }
+      if (lane == 0 && blockIdx.x < kProfCtas && (warp == kDequantWarp0 || warp == kDequantWarp0 + kDequantWarps - 1)) {
+        const int base = (warp == kDequantWarp0) ? 6 : 10;   // first and last dequantiser warp
+        for (int i = 0; i < 3; ++i) g_wait_prof[blockIdx.x][base + i] = prof_acc[6 + i];
+        g_wait_prof[blockIdx.x][base + 3] = clock64() - prof_t0;
+      }
 #endif
+    };
+    if (half) dequantise(std::true_type{});
+    else dequantise(std::false_type{});
   } else if (warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + 4) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
@@ -418,24 +568,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
       const int n_rows = u.rows, npad = u.npad;
       const int buf = (nbuf == 2) ? (unit_it & 1) : 0;
       const float sc = p.ph[u.phase].gs[u.slot] * 256.0f;
+      // down units: the routes and routing weights of 32 of the item's rows at a time, one row per
+      // lane, broadcast by shuffles below.  The first 32 are loaded before the accumulators are waited
+      // for, the next 32 while the current ones are stored: a load per row inside the store loop
+      // would put a round trip to L2 between every two rows' stores.
+      int cur_rt = -1, nxt_rt = -1;
+      float cur_rw = 1.0f, nxt_rw = 1.0f;
+      if (u.phase == 1 && lane < n_rows) {
+        cur_rt = p.sorted[u.pos0 + lane];
+        if (p.weighted) cur_rw = p.wsorted[u.pos0 + lane];
+      }
       if (!mbar_wait<2000>(bar_accfull + 8 * buf, (unit_it / nbuf) & 1, abort_flag, kWaitEpiAccFull)) break;
       tc_fence_after();
-      const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * acc_buf_stride;     // tile 0, K block 0
-      const uint32_t d1 = d0 + 4 * p.ncap;                                        // tile 1, K block 0
+      const bool wide = half && npad > 16;
+      // narrow: tile 0 / tile 1, K block 0 (the other K blocks acols columns further each); wide: the tiles' accumulators
+      const uint32_t d0 = tmem + lane_off + kAccCol0 + buf * acc_buf_stride;
+      const uint32_t d1 = d0 + (wide ? kWideAccCols : 4 * acols);
       for (int c0 = 0; c0 < npad; c0 += 16) {
         uint32_t a[16], b[16];
-        {
-          // ((K block 0 + 1) + 2) + 3 for each tile: the same order for every shape
+        tmem_ld16(d0 + c0, a);
+        tmem_ld16(d1 + c0, b);
+        if (wide) {
+          tmem_wait_ld();
+        } else {
+          // ((K block 0 + 1) + 2) + 3 for each tile: the same order for every narrow shape
           uint32_t t[16];
-          tmem_ld16(d0 + c0, a);
-          tmem_ld16(d1 + c0, b);
 #pragma unroll
           for (int part = 1; part < 4; ++part) {
-            tmem_ld16(d0 + part * p.ncap + c0, t);
+            tmem_ld16(d0 + part * acols + c0, t);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j) a[j] = __float_as_uint(__uint_as_float(a[j]) + __uint_as_float(t[j]));
-            tmem_ld16(d1 + part * p.ncap + c0, t);
+            tmem_ld16(d1 + part * acols + c0, t);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j) b[j] = __float_as_uint(__uint_as_float(b[j]) + __uint_as_float(t[j]));
@@ -447,23 +611,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
           mbar_arrive_if(bar_accempty + 8 * buf, lane0);
         }
         if (c0 < n_rows) {
+          if (u.phase == 0) {
+            uint16_t* dst = p.inter + static_cast<size_t>(u.pos0 + c0) * p.I + u.pair * kTileRows + row;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int n = c0 + j;
-            if (n < n_rows) {
-              const float va = __uint_as_float(a[j]) * sc;
-              const float vb = __uint_as_float(b[j]) * sc;
-              if (u.phase == 0) {
+            for (int j = 0; j < 16; ++j) {
+              if (c0 + j < n_rows) {
+                const float va = __uint_as_float(a[j]) * sc;
+                const float vb = __uint_as_float(b[j]) * sc;
                 const float act = va / (1.0f + __expf(-va)) * vb;
-                p.inter[static_cast<size_t>(u.pos0 + n) * p.I + u.pair * kTileRows + row] =
-                    __bfloat16_as_ushort(__float2bfloat16_rn(act));
-              } else {
-                const int route = p.sorted[u.pos0 + n];
-                const float wgt = p.weighted ? p.wsorted[u.pos0 + n] : 1.0f;
-                float* dst = p.y + static_cast<size_t>(route) * p.H + u.pair * 2 * kTileRows + row;
-                dst[0] = va * wgt;
-                dst[kTileRows] = vb * wgt;
+                dst[static_cast<size_t>(j) * p.I] = __bfloat16_as_ushort(__float2bfloat16_rn(act));
               }
+            }
+          } else {
+            if ((c0 & 16) == 0) {
+              nxt_rt = -1;
+              nxt_rw = 1.0f;
+              if (c0 + 32 + lane < n_rows) {
+                nxt_rt = p.sorted[u.pos0 + c0 + 32 + lane];
+                if (p.weighted) nxt_rw = p.wsorted[u.pos0 + c0 + 32 + lane];
+              }
+            }
+            float* ybase = p.y + u.pair * 2 * kTileRows + row;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int route = __shfl_sync(0xffffffffu, cur_rt, (c0 & 16) + j);     // -1 beyond the item's rows
+              const float wgt = __shfl_sync(0xffffffffu, cur_rw, (c0 & 16) + j);
+              if (route >= 0) {
+                float* dst = ybase + static_cast<size_t>(route) * p.H;
+                dst[0] = __uint_as_float(a[j]) * sc * wgt;
+                dst[kTileRows] = __uint_as_float(b[j]) * sc * wgt;
+              }
+            }
+            if (c0 & 16) {
+              cur_rt = nxt_rt;
+              cur_rw = nxt_rw;
             }
           }
         }
@@ -607,22 +788,13 @@ extern "C" int okc_moe_debug_wait_profile(long long* host_out) {
 }
 #endif
 
-size_t gemm_smem_bytes(int n_stages, int ncap) {
-  return 1024 + static_cast<size_t>(n_stages) * (kStageBytes + static_cast<size_t>(ncap) * 512) + sizeof(Ctrl);
-}
-
-int gemm_stages_for(int ncap) {
-  // 227 KB of shared memory per CTA
-  const size_t budget = 232448 - 1024 - sizeof(Ctrl);
-  int n = static_cast<int>(budget / (kStageBytes + static_cast<size_t>(ncap) * 512));
-  return n > kMaxStages ? kMaxStages : n;
-}
+static_assert(sizeof(Ctrl) <= kGemmCtrlReserve, "the control block outgrew its reserve");
 
 cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream) {
-  const size_t smem = gemm_smem_bytes(p.n_stages, p.ncap);
-  cudaError_t e = cudaFuncSetAttribute(okc_moe_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  // always the whole 227 KB: how the ring divides it is decided on the device from the step's widest item
+  cudaError_t e = cudaFuncSetAttribute(okc_moe_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
   if (e != cudaSuccess) return e;
-  return launch_kernel(okc_moe_gemm, dim3(grid), dim3(kGemmThreads), smem, stream, true, p);
+  return launch_kernel(okc_moe_gemm, dim3(grid), dim3(kGemmThreads), kSmemBudget, stream, true, p);
 }
 
 // The combine without the post-expert norm needs no row-wide reduction, so a token's row is cut

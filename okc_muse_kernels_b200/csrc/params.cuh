@@ -52,7 +52,7 @@ cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t stream);
 // One of the two GEMM phases of a step: 0 = gate_up on w13 (token operand xg), 1 = down on w2
 // (token operand inter).
 struct PhaseParams {
-  CUtensorMap bmap[2];        // token operand [rows, K] bf16, box = 64 elements x {16, 32} rows
+  CUtensorMap bmap[3];        // token operand [rows, K] bf16, box = 64 elements x {16, 32, 64} rows
   const uint8_t* wpacked;     // stage images of every expert slot
   const float* gs;            // [slots] global scales
   int pairs;                  // units per work item
@@ -69,8 +69,6 @@ struct MoeGemmParams {
   int32_t* work_counter;      // next unit of this launch (zeroed by the gather kernel)
   int32_t* done;              // [items] epilogue warps that finished a gate_up unit of the item
   int phase_lo, phase_hi;
-  int n_stages;               // shared-memory ring depth
-  int ncap;                   // largest padded token count (sizes the B part of a stage)
   uint16_t* inter;            // bf16 [Rpad, I]     (phase 0 output, phase 1 token operand)
   int I;
   float* y;                   // f32 [R, H]         (phase 1 output)
@@ -80,7 +78,6 @@ struct MoeGemmParams {
   int weighted;
 };
 cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream);
-int gemm_stages_for(int ncap);
 
 // The exchange kernels of the expert-parallel step (ep.cu).
 struct EpParams {
@@ -128,6 +125,5 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
-size_t gemm_smem_bytes(int n_stages, int ncap);
 
 }  // namespace okc

@@ -27,6 +27,11 @@ extern "C" int okc_moe_debug_route_profile(long long* host_out) {
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
+__device__ __forceinline__ int items_of(int c, int cmax, int chunk) {
+  const int per = item_rows(c, cmax, chunk);
+  return (c + per - 1) / per;
+}
+
 // Router logits from the token rows: part[ks][t][e] = sum over the K range of split ks of
 // hidden[t][k] * w[e][k], FP32 multiply-adds in ascending k (bf16 -> f32 is exact).  The step before
 // the MoE path in the reference's layer (muse_decode_layer/layer.py:325-351, _router_split), fused
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
   }
 
   OKC_ROUTE_MARK(4)
-  // ---- 5. work items: experts by load descending (ties by id), cut into runs of <= chunk_rows rows
+  // ---- 5. work items: experts by load descending (ties by id), cut into runs of item_rows() rows
   int active = 0;
   for (int e = tid; e < p.slots; e += kRouteThreads) {
     const int c = cnt[e];
@@ -318,12 +323,13 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
   __syncthreads();
   OKC_ROUTE_MARK(5)
   const int n_active = s_nact;
+  const int cmax = n_active > 0 ? cnt[order[0]] : 0;     // the heaviest expert decides whether the step is a wide one
   if (warp == 0) {
     const int per = (n_active + 31) >> 5;
     int local = 0;
     for (int j = 0; j < per; ++j) {
       const int r = lane * per + j;
-      if (r < n_active) local += (cnt[order[r]] + p.chunk_rows - 1) / p.chunk_rows;
+      if (r < n_active) local += items_of(cnt[order[r]], cmax, p.chunk_rows);
     }
     int incl = local;
 #pragma unroll
@@ -334,7 +340,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     int run = incl - local;
     for (int j = 0; j < per; ++j) {
       const int r = lane * per + j;
-      if (r < n_active) { ibase[r] = run; run += (cnt[order[r]] + p.chunk_rows - 1) / p.chunk_rows; }
+      if (r < n_active) { ibase[r] = run; run += items_of(cnt[order[r]], cmax, p.chunk_rows); }
     }
     if (lane == 31) {
       p.meta[kMetaItems] = incl < p.max_items ? incl : p.max_items;
@@ -342,6 +348,8 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
       p.meta[kMetaStatus] = 0;
       p.meta[kMetaDetail] = 0;
       p.meta[kMetaTokens] = p.T;
+      // the widest item is the first one of the heaviest expert
+      p.meta[kMetaWcap] = item_pad(min(cmax, item_rows(cmax, cmax, p.chunk_rows)));
     }
   }
   __syncthreads();
@@ -349,11 +357,10 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     const int e = order[r];
     const int c = cnt[e];
     int it = ibase[r];
-    for (int c0 = 0; c0 < c && it < p.max_items; c0 += p.chunk_rows, ++it) {
-      const int n = min(p.chunk_rows, c - c0);
-      int npad = 16;
-      while (npad < n) npad <<= 1;
-      p.items[it] = make_int4(e, offs[e] + c0, n, npad);
+    const int per = item_rows(c, cmax, p.chunk_rows);
+    for (int c0 = 0; c0 < c && it < p.max_items; c0 += per, ++it) {
+      const int n = min(per, c - c0);
+      p.items[it] = make_int4(e, offs[e] + c0, n, item_pad(n));
     }
   }
   OKC_ROUTE_MARK(6)

@@ -135,7 +135,8 @@ def check_routing(ids: np.ndarray, biased: np.ndarray, k: int, local_start: int 
     return None
 
 
-def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int = 16):
+def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int = 16, narrow: int = 32,
+                wide: int = 64):
     """Token -> expert sort of the local routes.
 
     Route index i = t*k + slot.  Returns a dict with
@@ -144,7 +145,10 @@ def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int 
       sorted   int32 [n_local]       route indices in (expert, route index) order
       pos      int32 [T*k]           position of each route in ``sorted`` (-1 if not local)
       items    int32 [n_items, 3]    (local expert, first position, rows) work items: experts by
-                                     load descending (ties by id), each cut into runs of <= chunk rows
+                                     load descending (ties by id), each cut into runs of <= chunk rows;
+                                     but when some expert has more than ``narrow`` rows, an expert with
+                                     at most 16 rows is one item and every other one is cut into runs of
+                                     <= wide rows
     """
     ids = np.asarray(ids, dtype=np.int64)
     flat = ids.reshape(-1)
@@ -160,9 +164,11 @@ def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int 
     pos[sorted_routes] = np.arange(sorted_routes.shape[0], dtype=np.int32)
     active = [e for e in np.argsort(-counts.astype(np.int64), kind="stable") if counts[e] > 0]
     items = []
+    cmax = int(counts.max()) if counts.size else 0
     for e in active:
-        for c0 in range(0, int(counts[e]), chunk):
-            items.append((int(e), int(offsets[e]) + c0, min(chunk, int(counts[e]) - c0)))
+        per = chunk if cmax <= narrow else (16 if int(counts[e]) <= 16 else wide)
+        for c0 in range(0, int(counts[e]), per):
+            items.append((int(e), int(offsets[e]) + c0, min(per, int(counts[e]) - c0)))
     return {"counts": counts, "offsets": offsets, "sorted": sorted_routes, "pos": pos,
             "items": np.asarray(items, dtype=np.int32).reshape(-1, 3)}
 

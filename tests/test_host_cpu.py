@@ -131,8 +131,8 @@ def test_softmax_topk_oracle_properties():
 def test_sort_oracle_is_stable_and_chunks_items():
     rng = np.random.default_rng(5)
     ids = rng.integers(0, 16, (300, 4)).astype(np.int32)
-    ids[:, 0] = 3                                              # one hot expert: 300 rows -> 3 items
-    s = moe_np.sort_routes(ids, local_start=2, local_count=8, chunk=128)
+    ids[:, 0] = 3                                              # one hot expert: 300+ rows -> a wide step, 64-row items
+    s = moe_np.sort_routes(ids, local_start=2, local_count=8, chunk=32)
     assert s["counts"].sum() == ((ids >= 2) & (ids < 10)).sum()
     flat = ids.reshape(-1)
     srt = s["sorted"]
@@ -145,10 +145,15 @@ def test_sort_oracle_is_stable_and_chunks_items():
     assert np.all(s["pos"][(flat < 2) | (flat >= 10)] == -1)
     items = s["items"]
     hot = 300 + int((ids[:, 1:] == 3).sum())                   # expert 3 is local slot 1
-    n_hot = -(-hot // 128)
+    n_hot = -(-hot // 64)
     assert np.all(items[:n_hot, 0] == 1)
-    assert list(items[:n_hot, 2]) == [128] * (n_hot - 1) + [hot - 128 * (n_hot - 1)]
-    assert list(items[:n_hot, 1]) == [int(s["offsets"][1]) + 128 * i for i in range(n_hot)]
+    assert list(items[:n_hot, 2]) == [64] * (n_hot - 1) + [hot - 64 * (n_hot - 1)]
+    assert list(items[:n_hot, 1]) == [int(s["offsets"][1]) + 64 * i for i in range(n_hot)]
+    # the other experts (about 110 rows each) are cut into 64-row items too; in a step without such an
+    # expert the same call cuts into runs of `chunk` rows
+    assert all(n <= 64 for n in items[:, 2])
+    few = moe_np.sort_routes(ids[:20, 1:], local_start=2, local_count=8, chunk=16)
+    assert few["counts"].max() <= 32 and all(n <= 16 for n in few["items"][:, 2])
     loads = [s["counts"][e] for e in items[:, 0]]
     assert all(loads[i] >= loads[i + 1] for i in range(len(loads) - 1))
 
