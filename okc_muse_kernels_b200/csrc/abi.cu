@@ -252,8 +252,8 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   // unit waiting for the gate_up units of its own work item only.
   MoeGemmParams a;
   memset(&a, 0, sizeof(a));
-  const uint32_t boxes[3] = {16, 32, 64};
-  for (int i = 0; i < 3; ++i) {
+  const uint32_t boxes[5] = {4, 8, 16, 32, 64};
+  for (int i = 0; i < 5; ++i) {
     if (!encode_rows_map(&a.ph[0].bmap[i], w.xg, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.H), boxes[i])) return OKC_ERR_CUDA;
     if (!encode_rows_map(&a.ph[1].bmap[i], w.inter, static_cast<uint64_t>(g.Rpad), static_cast<uint64_t>(g.I), boxes[i])) return OKC_ERR_CUDA;
   }

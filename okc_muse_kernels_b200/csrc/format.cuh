@@ -13,29 +13,47 @@ constexpr int kTileRows = 128;                 // rows of one weight tile = M of
 constexpr int kStageK = 256;                   // K elements per shared-memory stage
 constexpr int kChunkK = 32;                    // K elements one thread dequantises per tcgen05.st
 constexpr int kChunks = kStageK / kChunkK;     // 8
-constexpr int kTileCodeBytes = kChunks * kTileRows * 16;   // 16384
-constexpr int kTileScaleBytes = kChunks * kTileRows * 2;   // 2048
-constexpr int kTileBytes = kTileCodeBytes + kTileScaleBytes;
-constexpr int kStageBytes = 2 * kTileBytes;    // 36864: two tiles (gate+up, or two row tiles of w2)
+// A stage image is two halves of 128 K elements; a half holds, for each of the two tiles (gate + up, or
+// two row tiles of w2), the codes of its four chunks and then their scales.  A whole stage is one
+// contiguous copy, and so is half a stage (the unit of the ring in a step with wide items).
+constexpr int kHalfChunks = kChunks / 2;                          // 4
+constexpr int kHalfTileCodeBytes = kHalfChunks * kTileRows * 16;  // 8192
+constexpr int kHalfTileScaleBytes = kHalfChunks * kTileRows * 2;  // 1024
+constexpr int kHalfTileBytes = kHalfTileCodeBytes + kHalfTileScaleBytes;   // 9216
+constexpr int kHalfStageBytes = 2 * kHalfTileBytes;               // 18432
+constexpr int kStageBytes = 2 * kHalfStageBytes;                  // 36864
+// byte offset of (tile, chunk, row) inside a stage image: codes (16 B) and scales (2 B)
+__host__ __device__ inline int stage_code_offset(int tile, int chunk, int row) {
+  return (chunk / kHalfChunks) * kHalfStageBytes + tile * kHalfTileBytes + (chunk % kHalfChunks) * (kTileRows * 16) + row * 16;
+}
+__host__ __device__ inline int stage_scale_offset(int tile, int chunk, int row) {
+  return (chunk / kHalfChunks) * kHalfStageBytes + tile * kHalfTileBytes + kHalfTileCodeBytes +
+         (chunk % kHalfChunks) * (kTileRows * 2) + row * 2;
+}
 constexpr int kNarrowRows = 32;                // most rows (tokens) of a narrow work item
 constexpr int kChunkRows = 64;                 // most rows of any work item (a wide one)
-// Work items.  While no expert of the step has more than 32 rows, every expert becomes narrow items of
-// at most chunk_rows_for() rows: 16 while the step is decode-sized or an expert gets 8 rows or fewer on
-// average (the accumulators of eight issuers then fit TMEM twice, so the epilogue overlaps the next
-// unit, and the stage ring is a stage deeper); 32 beyond, where 16-row items would stream and
-// dequantise most experts' weights twice.
-// A step in which some expert has more than 32 rows is a wide step: an expert is cut into items of 64
-// rows, what is left over at its end being one more item; items of up to 16 rows are narrow ones, all
-// others wide ones padded to 32 or 64 rows (one accumulator per tile: two wide items' accumulators, or
-// two 16-row items' partial sums, fit TMEM side by side, so the epilogue always overlaps the next unit).
+// Work items.  Normally every expert becomes narrow items of at most chunk_rows_for() rows: 16 while the
+// step is decode-sized or an expert gets 8 rows or fewer on average (the accumulators of eight issuers then
+// fit TMEM twice, so the epilogue overlaps the next unit, and the stage ring is a stage deeper); 32 beyond,
+// where 16-row items would stream and dequantise most experts' weights twice.
+// A step can instead be a wide step: an expert is cut into items of 64 rows, what is left over at its end
+// being one more item; items of up to 16 rows are narrow ones, all others wide ones padded to 32 or 64
+// rows (one accumulator per tile: two wide items' accumulators, or two 16-row items' partial sums, fit
+// TMEM side by side, so the epilogue always overlaps the next unit).  A wide step runs on half-stage ring
+// slots, which costs its narrow items a few per cent; the sort kernel makes a step a wide one when some
+// expert has more than 32 rows and the wide cut has at least a tenth fewer items than the narrow one
+// (wide_step_pays).
 __host__ __device__ inline int chunk_rows_for(int T, int k, int E) {
   return (T <= 64 || static_cast<long long>(T) * k <= 8LL * E) ? 16 : kNarrowRows;
 }
 __host__ __device__ inline int item_pad(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
-// rows per item of an expert with c rows; cmax = rows of the step's heaviest expert, chunk = chunk_rows_for()
-__host__ __device__ inline int item_rows(int c, int cmax, int chunk) {
-  if (cmax <= kNarrowRows) return chunk;
+// rows per item of an expert with c rows; chunk = chunk_rows_for()
+__host__ __device__ inline int item_rows(int c, bool wide_step, int chunk) {
+  if (!wide_step) return chunk;
   return c <= 16 ? 16 : kChunkRows;
+}
+__host__ __device__ inline bool wide_step_pays(int cmax, long long items_narrow, long long items_wide) {
+  return cmax > kNarrowRows && 11 * items_wide <= 10 * items_narrow;
 }
 
 // Shared memory of the grouped-GEMM kernel: a reserve for its control block and the 1024-byte alignment

@@ -24,9 +24,9 @@
 //                 activation, store
 //
 // Work items are "narrow" (N = 16 or 32: the K blocks of a stage spread over eight issuers with a
-// partial accumulator each) or, in a step where some expert has more than 32 rows, "wide" (N = 32 or
-// 64, one issuer and one accumulator per tile, so that an expert with hundreds of rows is streamed
-// and dequantised once per 64 rows).  The geometry of a launch (ring slot size and depth, accumulator
+// partial accumulator each) or, in a step that the sort kernel made a wide one because experts with
+// many rows dominate it, "wide" (N = 32 or 64, one issuer and one accumulator per tile, so that an
+// expert with hundreds of rows is streamed and dequantised once per 64 rows).  The geometry of a launch (ring slot size and depth, accumulator
 // buffers) follows the widest item of the step, which the sort kernel leaves in the workspace.
 //
 // The reference computes the same products with mma.sync / wgmma on Hopper
@@ -86,7 +86,7 @@ struct UnitDesc {
   int slot;       // expert slot (weights, global scale)
   int pos0;       // first row of the item in the sorted route order
   int rows;       // token rows of the item
-  int npad;       // rows padded to 16 or 32 (N of the MMAs)
+  int npad;       // rows padded to 16, 32 or 64 (N of the MMAs)
   int pair;       // tile pair within the expert
   int item;       // work item index
   int stages;     // K / 256 of this phase
@@ -95,7 +95,11 @@ struct UnitDesc {
 struct Ctrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t a_full[2 * kASlots];     // [slot][tile]: the four dequantiser warps of one tile filled the slot
+  uint64_t a_full[2 * kASlots];     // [slot][tile]: the four dequantiser warps of one tile filled the slot (narrow unit)
+  uint64_t a_full_w[2 * kASlots];   // the same for wide units.  A barrier of its own per kind of unit, because
+                                    // a parity wait only tells phases one apart: every barrier needs to have one
+                                    // waiter, the thread whose MMAs let the next phase begin.  A thread that only
+                                    // looked on while another one issued would miss phases.
   uint64_t a_empty[2 * kASlots];    // [slot][tile]: that tile's MMAs on the slot completed
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
@@ -140,6 +144,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
   // shared-memory addresses of the barrier arrays (element i is 8 bytes further)
   const uint32_t bar_full = smem_u32(&ctrl->full[0]), bar_empty = smem_u32(&ctrl->empty[0]);
   const uint32_t bar_afull = smem_u32(&ctrl->a_full[0]), bar_aempty = smem_u32(&ctrl->a_empty[0]);
+  const uint32_t bar_afullw = smem_u32(&ctrl->a_full_w[0]);
   const uint32_t bar_accfull = smem_u32(&ctrl->acc_full[0]), bar_accempty = smem_u32(&ctrl->acc_empty[0]);
   const uint32_t bar_ufull = smem_u32(&ctrl->u_full[0]), bar_uempty = smem_u32(&ctrl->u_empty[0]);
 
@@ -150,6 +155,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
     }
     for (int i = 0; i < 2 * kASlots; ++i) {
       mbar_init(bar_afull + 8 * i, 4);             // the four lane quarters of one tile
+      mbar_init(bar_afullw + 8 * i, 4);
       mbar_init(bar_aempty + 8 * i, 1);            // that tile's issuer for this K block
     }
     for (int i = 0; i < 2; ++i) {
@@ -202,7 +208,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       for (int ph = 0; ph < 2; ++ph)
-        for (int i = 0; i < 3; ++i) tma_prefetch_desc(&p.ph[ph].bmap[i]);
+        for (int i = 0; i < 5; ++i) tma_prefetch_desc(&p.ph[ph].bmap[i]);
       const uint64_t pol = policy_evict_first();
       const int n_items = p.meta[kMetaItems];
       const int units0 = n_items * p.ph[0].pairs, units1 = n_items * p.ph[1].pairs;
@@ -231,27 +237,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
         u.pair = gl - u.item * pp.pairs;
         const int4 wi = p.items[u.item];
         u.slot = wi.x; u.pos0 = wi.y; u.rows = wi.z; u.npad = wi.w; u.stages = pp.stages;
+        // Only the item's own rows are copied (in boxes of 4 ... 64 rows): the MMAs run over npad rows of
+        // the slot, what lies behind the copied ones is left over from earlier stages and only reaches
+        // accumulator columns that the epilogue never reads.  At a few rows per expert the padding would
+        // otherwise be a sixth of all bytes the SM takes in.
+        const int mi = (u.rows <= 4) ? 0 : (u.rows <= 8) ? 1 : (u.rows <= 16) ? 2 : (u.rows <= 32) ? 3 : 4;
+        const int brows = 4 << mi;                               // token rows copied per stage
         ctrl->units[k] = u;
         mbar_arrive(bar_ufull + 8 * k);
-        const int mi = (u.npad == 16) ? 0 : (u.npad == 32) ? 1 : 2;
         const uint8_t* src = pp.wpacked + static_cast<size_t>(u.slot) * pp.expert_bytes +
                              static_cast<size_t>(u.pair) * pp.stages * kStageBytes;
         const int steps = pp.stages * sps;                       // ring slots this unit goes through
-        const uint32_t tx_bytes = half ? kStageBytes / 2 + u.npad * 256 : kStageBytes + u.npad * 512;
+        const uint32_t tx_bytes = half ? kHalfStageBytes + brows * 256 : kStageBytes + brows * 512;
         // weights of ring step r of the unit -> slot at dst
         auto send_weights = [&](int r, uint32_t dst, uint32_t bar) {
-          if (!half) {
-            bulk_g2s_hint(dst, src + static_cast<size_t>(r) * kStageBytes, kStageBytes, bar, pol);
-          } else {
-            const uint8_t* sp = src + static_cast<size_t>(r >> 1) * kStageBytes;
-            const int hh = r & 1;
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              bulk_g2s_hint(dst + t * (kTileBytes / 2), sp + t * kTileBytes + hh * (kTileCodeBytes / 2), kTileCodeBytes / 2, bar, pol);
-              bulk_g2s_hint(dst + t * (kTileBytes / 2) + kTileCodeBytes / 2,
-                            sp + t * kTileBytes + kTileCodeBytes + hh * (kTileScaleBytes / 2), kTileScaleBytes / 2, bar, pol);
-            }
-          }
+          if (!half) bulk_g2s_hint(dst, src + static_cast<size_t>(r) * kStageBytes, kStageBytes, bar, pol);
+          else bulk_g2s_hint(dst, src + static_cast<size_t>(r) * kHalfStageBytes, kHalfStageBytes, bar, pol);
         };
         // token rows of ring step r -> behind the weights of the slot
         auto send_tokens = [&](int r, uint32_t dst, uint32_t bar) {
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
           } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              tma_2d_g2s(dst + kStageBytes / 2 + j * u.npad * 128, &pp.bmap[mi], (r >> 1) * kStageK + ((r & 1) * 2 + j) * 64, u.pos0, bar);
+              tma_2d_g2s(dst + kHalfStageBytes + j * u.npad * 128, &pp.bmap[mi], (r >> 1) * kStageK + ((r & 1) * 2 + j) * 64, u.pos0, bar);
           }
         };
         int r_begin = 0;
@@ -344,9 +345,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
         const int tile = warp & 1, kb = warp >> 1;
         const uint32_t my_afull = bar_afull + 16 * kb + 8 * tile, my_aempty = bar_aempty + 16 * kb + 8 * tile;
         const uint32_t a0 = tmem + kb * kASlotCols + tile * 32;
-        const uint32_t b_off = kHalf ? kStageBytes / 2 : kStageBytes;    // token rows behind the weights of a slot
+        const uint32_t b_off = kHalf ? kHalfStageBytes : kStageBytes;    // token rows behind the weights of a slot
         int st = 0;
-        uint32_t ph = 0, sph = 0;     // ring phase; A-slot phase (flips once per stage)
+        uint32_t ph = 0;              // ring phase
+        uint32_t sph = 0, sphw = 0;   // A-slot phases: narrow units' barriers, wide units' barriers (flip once per stage of that kind)
         OKC_PROF_DECL
         const uint32_t desc_hi = static_cast<uint32_t>(smem_desc_sw128(0) >> 32);
         const uint32_t desc_lo_const = static_cast<uint32_t>(smem_desc_sw128(0));
@@ -386,14 +388,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
                 }
                 if (++st == NS) { st = 0; ph ^= 1; }
               }
-              if (kHalf && kb == 0) {
-                // In a wide step this thread issues for all four A slots of its tile whenever the unit is a
-                // wide one.  A parity wait only tells phases one apart, so it keeps step with the other
-                // three slots in narrow units too: it sees every phase of their barriers complete.
-#pragma unroll
-                for (int k4 = 1; k4 < kASlots; ++k4)
-                  if (!OKC_PROF_WAIT(4, mbar_wait<200>(bar_afull + 16 * k4 + 8 * tile, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
-              }
               sph ^= 1;
             }
             if (elect_one()) mma_commit(bar_accfull + 8 * buf);
@@ -411,7 +405,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                   const int k4 = 2 * hh + j;
-                  if (!OKC_PROF_WAIT(4, mbar_wait(bar_afull + 16 * k4 + 8 * tile, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
+                  if (!OKC_PROF_WAIT(4, mbar_wait(bar_afullw + 16 * k4 + 8 * tile, sphw, abort_flag, kWaitMmaAFull))) goto issuer_done;
                   tc_fence_after();
                   const uint32_t a = a_tile + k4 * kASlotCols;
                   if (elect_one()) {
@@ -428,24 +422,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
                 }
                 if (++st == NS) { st = 0; ph ^= 1; }
               }
-              sph ^= 1;
+              sphw ^= 1;
             }
             if (elect_one()) mma_commit(bar_accfull + 8 * buf);
             __syncwarp();
           } else {
-            // wide item, an issuer without MMAs of its own: keeps the ring's and the accumulator's barrier
-            // counts.  It also waits for its A slot of every stage as if it had MMAs to issue: a parity
-            // wait only tells phases one apart, so a thread that will wait on that barrier again in the
-            // next narrow unit must never run more than one stage ahead of it.
-            for (int s = 0; s < u.stages; ++s) {
-#pragma unroll
-              for (int hh = 0; hh < 2; ++hh) {
-                if (!OKC_PROF_WAIT(3, mbar_wait<200>(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) goto issuer_done;
-                if (hh == (kb >> 1) && !OKC_PROF_WAIT(4, mbar_wait<200>(my_afull, sph, abort_flag, kWaitMmaAFull))) goto issuer_done;
-                mbar_arrive_if(bar_empty + 8 * st, lane0);
-                if (++st == NS) { st = 0; ph ^= 1; }
-              }
-              sph ^= 1;
+            // wide item, an issuer without MMAs of its own: keeps the ring's and the accumulator's barrier counts
+            for (int r = 0; r < 2 * u.stages; ++r) {
+              if (!OKC_PROF_WAIT(3, mbar_wait<200>(bar_full + 8 * st, ph, abort_flag, kWaitMmaFull))) goto issuer_done;
+              mbar_arrive_if(bar_empty + 8 * st, lane0);
+              if (++st == NS) { st = 0; ph ^= 1; }
             }
             mbar_arrive_if(bar_accfull + 8 * buf, lane0);
           }
@@ -476,13 +462,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
     const uint32_t trow = tmem + (static_cast<uint32_t>(q * 32) << 16) + tile * 32;
     auto dequantise = [&](auto half_tag) {
       constexpr bool kHalf = decltype(half_tag)::value;
-      // a tile's part of a ring slot: codes [chunks][128 rows][16 B], then scales [chunks][128 rows][2 B];
-      // eight chunks (a whole stage) or four (half a stage)
-      constexpr uint32_t kSlotTile = kHalf ? kTileBytes / 2 : kTileBytes;
-      constexpr uint32_t kSlotCodes = kHalf ? kTileCodeBytes / 2 : kTileCodeBytes;
-      const uint32_t code_off = tile * kSlotTile + row * 16;
-      const uint32_t scale_off = tile * kSlotTile + kSlotCodes + row * 2;
-      const uint32_t my_afull = bar_afull + 8 * tile, my_aempty = bar_aempty + 8 * tile;
+      // this thread's row in its tile's part of a half stage: codes [4 chunks][128 rows][16 B], then
+      // scales [4 chunks][128 rows][2 B]; its group's K block is chunks 2 grp, 2 grp + 1 of the half
+      const uint32_t code_off = tile * kHalfTileBytes + (2 * grp) * (kTileRows * 16) + row * 16;
+      const uint32_t scale_off = tile * kHalfTileBytes + kHalfTileCodeBytes + (2 * grp) * (kTileRows * 2) + row * 2;
+      const uint32_t my_aempty = bar_aempty + 8 * tile;
       int st = 0;
       // barrier of the A slot stored to but not yet handed over; a barrier nobody waits on stands in
       // before the first slot, so the hand-over below needs no "is anything pending" test
@@ -491,6 +475,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
       OKC_PROF_DECL
       UnitDesc u;
       for (uint32_t unit_it = 0; next_unit<true>(ctrl, bar_ufull, bar_uempty, unit_it, lane0, abort_flag, kWaitDqUnit, u); ++unit_it) {
+        // the slots of a wide unit are handed to the tile's one issuer through barriers of their own
+        const uint32_t my_afull = ((kHalf && u.npad > 16) ? bar_afullw : bar_afull) + 8 * tile;
         for (int s = 0; s < u.stages; ++s) {
 #pragma unroll
           for (int hh = 0; hh < (kHalf ? 2 : 1); ++hh) {
@@ -500,13 +486,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
               const uint32_t simg = smem0 + st * slot_bytes + scale_off;
 #pragma unroll
               for (int h = 0; h < (kHalf ? 1 : 2); ++h) {
-                // whole stages: this group's two K blocks of the stage; half stages: its K block of this half
-                const int kb = kHalf ? 2 * hh + grp : grp + 2 * h;
-                const int c0 = kHalf ? 2 * grp : 2 * kb;         // first of the slot's two chunks within the ring slot
+                // this group's K block of half h of the stage (whole-stage slots) or of this half (half-stage slots)
+                const int kb = 2 * (kHalf ? hh : h) + grp;
+                const uint32_t hoff = kHalf ? 0u : h * kHalfStageBytes;
                 // this thread's 64 K elements of the slot: two chunks of 16 code bytes + 2 scale bytes
-                const uint4 w0 = *reinterpret_cast<const uint4*>(img + code_off + c0 * (kTileRows * 16));
-                const uint4 w1 = *reinterpret_cast<const uint4*>(img + code_off + (c0 + 1) * (kTileRows * 16));
-                const uint32_t sp0 = simg + c0 * (kTileRows * 2);
+                const uint4 w0 = *reinterpret_cast<const uint4*>(img + hoff + code_off);
+                const uint4 w1 = *reinterpret_cast<const uint4*>(img + hoff + code_off + kTileRows * 16);
+                const uint32_t sp0 = simg + hoff;
                 const uint32_t sp1 = sp0 + kTileRows * 2;
                 const uint32_t s00 = lds_u8(sp0), s01 = lds_u8(sp0 + 1), s10 = lds_u8(sp1), s11 = lds_u8(sp1 + 1);
                 uint32_t r[16];
@@ -783,6 +769,14 @@ cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t
 // host_out: long long [256][16] = per CTA of the last launch:
 // 0 producer total, 1 producer wait-empty, 2 mma wait acc-empty, 3 mma wait full, 4 mma wait a-full, 5 mma total,
 // 6..9 first dequantiser warp: wait full, wait a-empty, wait tcgen05.st, total; 10..13 the same for the last one.
+extern "C" int okc_moe_debug_stuck(int* host_out, int clear) {
+  if (cudaMemcpyFromSymbol(host_out, g_stuck, sizeof(g_stuck)) != cudaSuccess) return -3;
+  if (clear) {
+    void* dptr = nullptr;
+    if (cudaGetSymbolAddress(&dptr, g_stuck) != cudaSuccess || cudaMemset(dptr, 0, sizeof(g_stuck)) != cudaSuccess) return -3;
+  }
+  return 0;
+}
 extern "C" int okc_moe_debug_wait_profile(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, g_wait_prof, sizeof(g_wait_prof)) == cudaSuccess ? 0 : -3;
 }

@@ -52,7 +52,7 @@ cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t stream);
 // One of the two GEMM phases of a step: 0 = gate_up on w13 (token operand xg), 1 = down on w2
 // (token operand inter).
 struct PhaseParams {
-  CUtensorMap bmap[3];        // token operand [rows, K] bf16, box = 64 elements x {16, 32, 64} rows
+  CUtensorMap bmap[5];        // token operand [rows, K] bf16, box = 64 elements x {4, 8, 16, 32, 64} rows
   const uint8_t* wpacked;     // stage images of every expert slot
   const float* gs;            // [slots] global scales
   int pairs;                  // units per work item

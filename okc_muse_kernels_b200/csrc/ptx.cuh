@@ -77,6 +77,21 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // its loop; nothing traps, the context stays usable and the host reads the code from the status
 // word.
 constexpr uint32_t kWaitLimit = 1u << 30;
+#ifdef OKC_WAIT_PROFILE
+// instrumented build: where every warp of a CTA was waiting when the CTA gave up
+// [cta][warp] = {code of the wait, barrier address, parity waited for, 1 = this wait ran out / 2 = another did}
+constexpr int kStuckCtas = 160;
+static __device__ int g_stuck[kStuckCtas][32][4];   // one copy per translation unit; the GEMM one is read back
+__device__ __forceinline__ void record_stuck(int code, uint32_t bar, uint32_t parity, int how) {
+  if ((threadIdx.x & 31) == 0 && blockIdx.x < kStuckCtas) {
+    int* e = g_stuck[blockIdx.x][threadIdx.x >> 5];
+    e[0] = code; e[1] = static_cast<int>(bar); e[2] = static_cast<int>(parity); e[3] = how;
+  }
+}
+#define OKC_RECORD_STUCK(code, bar, parity, how) record_stuck(code, bar, parity, how)
+#else
+#define OKC_RECORD_STUCK(code, bar, parity, how)
+#endif
 template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
                                           uint32_t limit_cycles = kWaitLimit) {
@@ -91,9 +106,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (kSleepNs > 0) __nanosleep(kSleepNs);
       if (mbar_try(bar, parity)) return true;
     }
-    if (*abort_flag != 0) return false;
+    if (*abort_flag != 0) { OKC_RECORD_STUCK(code, bar, parity, 2); return false; }
     if (static_cast<uint32_t>(clock()) - t0 > limit_cycles) break;
   }
+  OKC_RECORD_STUCK(code, bar, parity, 1);
   atomicCAS(const_cast<int*>(abort_flag), 0, code);
   return false;
 }

@@ -52,9 +52,9 @@ __global__ void __launch_bounds__(256) okc_repack(const RepackParams p) {
     outw[2 * blk + 1] = static_cast<uint32_t>(o >> 32);
   }
   uint8_t* img = p.out + static_cast<size_t>(p.first_slot + ex) * p.expert_bytes +
-                 (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes + static_cast<size_t>(tile) * kTileBytes;
-  *reinterpret_cast<uint4*>(img + chunk * (kTileRows * 16) + row * 16) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-  *reinterpret_cast<uint16_t*>(img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2) =
+                 (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes;
+  *reinterpret_cast<uint4*>(img + stage_code_offset(tile, chunk, row)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+  *reinterpret_cast<uint16_t*>(img + stage_scale_offset(tile, chunk, row)) =
       static_cast<uint16_t>(stored[0]) | (static_cast<uint16_t>(stored[1]) << 8);
 }
 
@@ -69,10 +69,9 @@ __global__ void __launch_bounds__(256) okc_unpack(const UnpackParams p) {
   const int tile = static_cast<int>(r % 2); r /= 2;
   const int stage = static_cast<int>(r % p.stages); r /= p.stages;
   const int pair = static_cast<int>(r);
-  const uint8_t* img = p.packed + (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes +
-                       static_cast<size_t>(tile) * kTileBytes;
-  const uint4 w = *reinterpret_cast<const uint4*>(img + chunk * (kTileRows * 16) + row * 16);
-  const uint8_t* sc = img + kTileCodeBytes + chunk * (kTileRows * 2) + row * 2;
+  const uint8_t* img = p.packed + (static_cast<size_t>(pair) * p.stages + stage) * kStageBytes;
+  const uint4 w = *reinterpret_cast<const uint4*>(img + stage_code_offset(tile, chunk, row));
+  const uint8_t* sc = img + stage_scale_offset(tile, chunk, row);
   uint32_t regs[16];
   dequant_chunk(w, sc[0], sc[1], regs);
   const int dst_row = p.is_w13 ? (tile * p.inter + pair * kTileRows + row) : (pair * 2 * kTileRows + tile * kTileRows + row);

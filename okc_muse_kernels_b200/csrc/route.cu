@@ -27,8 +27,8 @@ extern "C" int okc_moe_debug_route_profile(long long* host_out) {
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
-__device__ __forceinline__ int items_of(int c, int cmax, int chunk) {
-  const int per = item_rows(c, cmax, chunk);
+__device__ __forceinline__ int items_of(int c, bool wide_step, int chunk) {
+  const int per = item_rows(c, wide_step, chunk);
   return (c + per - 1) / per;
 }
 
@@ -323,13 +323,29 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
   __syncthreads();
   OKC_ROUTE_MARK(5)
   const int n_active = s_nact;
-  const int cmax = n_active > 0 ? cnt[order[0]] : 0;     // the heaviest expert decides whether the step is a wide one
+  __shared__ int s_wide;
   if (warp == 0) {
     const int per = (n_active + 31) >> 5;
+    // narrow or wide step: the item counts of both cuts decide (the heaviest expert is order[0])
+    int n_narrow = 0, n_wide = 0;
+    for (int j = 0; j < per; ++j) {
+      const int r = lane * per + j;
+      if (r < n_active) {
+        n_narrow += items_of(cnt[order[r]], false, p.chunk_rows);
+        n_wide += items_of(cnt[order[r]], true, p.chunk_rows);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      n_narrow += __shfl_xor_sync(0xffffffffu, n_narrow, o);
+      n_wide += __shfl_xor_sync(0xffffffffu, n_wide, o);
+    }
+    const int cmax = n_active > 0 ? cnt[order[0]] : 0;
+    const bool wide_step = wide_step_pays(cmax, n_narrow, n_wide);
     int local = 0;
     for (int j = 0; j < per; ++j) {
       const int r = lane * per + j;
-      if (r < n_active) local += items_of(cnt[order[r]], cmax, p.chunk_rows);
+      if (r < n_active) local += items_of(cnt[order[r]], wide_step, p.chunk_rows);
     }
     int incl = local;
 #pragma unroll
@@ -340,24 +356,26 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RoutePa
     int run = incl - local;
     for (int j = 0; j < per; ++j) {
       const int r = lane * per + j;
-      if (r < n_active) { ibase[r] = run; run += items_of(cnt[order[r]], cmax, p.chunk_rows); }
+      if (r < n_active) { ibase[r] = run; run += items_of(cnt[order[r]], wide_step, p.chunk_rows); }
     }
     if (lane == 31) {
+      s_wide = wide_step ? 1 : 0;
       p.meta[kMetaItems] = incl < p.max_items ? incl : p.max_items;
       p.meta[kMetaLocalRoutes] = offs[p.slots];
       p.meta[kMetaStatus] = 0;
       p.meta[kMetaDetail] = 0;
       p.meta[kMetaTokens] = p.T;
       // the widest item is the first one of the heaviest expert
-      p.meta[kMetaWcap] = item_pad(min(cmax, item_rows(cmax, cmax, p.chunk_rows)));
+      p.meta[kMetaWcap] = item_pad(min(cmax, item_rows(cmax, wide_step, p.chunk_rows)));
     }
   }
   __syncthreads();
+  const bool wide_step = s_wide != 0;
   for (int r = tid; r < n_active; r += kRouteThreads) {
     const int e = order[r];
     const int c = cnt[e];
     int it = ibase[r];
-    const int per = item_rows(c, cmax, p.chunk_rows);
+    const int per = item_rows(c, wide_step, p.chunk_rows);
     for (int c0 = 0; c0 < c && it < p.max_items; c0 += per, ++it) {
       const int n = min(per, c - c0);
       p.items[it] = make_int4(e, offs[e] + c0, n, item_pad(n));

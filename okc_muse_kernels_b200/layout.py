@@ -12,9 +12,13 @@ A GEMM ``D[rows, tokens] = W[rows, K] . X[tokens, K]^T`` is cut into *units*: on
 of 128-row tiles (gate tile + matching up tile for w13; two adjacent tiles for w2).  A unit is
 streamed as K/256 *stages*; a stage is 36 864 contiguous bytes::
 
-    [tile A image 18 432 B][tile B image 18 432 B]
-    tile image = codes  [chunk c = 0..7][row r = 0..127][16 B]      (16 384 B)
-                 scales [chunk c = 0..7][row r = 0..127][ 2 B]      ( 2 048 B)
+    [half 0: K elements 0..127 of the stage, 18 432 B][half 1: K elements 128..255, 18 432 B]
+    half       = [tile A part 9 216 B][tile B part 9 216 B]
+    tile part  = codes  [chunk c = 0..3][row r = 0..127][16 B]      (8 192 B)
+                 scales [chunk c = 0..3][row r = 0..127][ 2 B]      (1 024 B)
+
+so that a whole stage and half a stage are both one contiguous copy (a step with experts of more
+than 32 rows streams half stages).
 
 Chunk c of row r holds K elements ``k0 + 32c .. k0 + 32c + 31`` (two 16-element scale blocks): four
 32-bit words ``(w0, w1)`` for block 0 and ``(w2, w3)`` for block 1, and the blocks' two scale bytes.
@@ -49,8 +53,12 @@ CHUNK_K = 32
 CHUNKS = STAGE_K // CHUNK_K                      # 8
 TILE_CODE_BYTES = CHUNKS * TILE_ROWS * 16        # 16384
 TILE_SCALE_BYTES = CHUNKS * TILE_ROWS * 2        # 2048
-TILE_BYTES = TILE_CODE_BYTES + TILE_SCALE_BYTES  # 18432
+TILE_BYTES = TILE_CODE_BYTES + TILE_SCALE_BYTES  # 18432: one tile's codes and scales of a stage
 STAGE_BYTES = 2 * TILE_BYTES                     # 36864
+HALF_CHUNKS = CHUNKS // 2                        # 4
+HALF_TILE_CODE_BYTES = TILE_CODE_BYTES // 2      # 8192
+HALF_TILE_BYTES = TILE_BYTES // 2                # 9216
+HALF_STAGE_BYTES = STAGE_BYTES // 2              # 18432
 
 OUT_MASK = 0x81C081C0
 # (source, op, amount) of the eight output registers; source 0 = w0, 1 = w1, 2 = u;
@@ -172,7 +180,9 @@ def scale_code_value(code: np.ndarray) -> np.ndarray:
 
 
 def pack_tile_stage(packed_rows: np.ndarray, sf_rows: np.ndarray) -> np.ndarray:
-    """One tile image: packed codes uint8 [128, 128] (K = 256) + scales uint8 [128, 16] -> uint8 [18432]."""
+    """One tile's codes [chunk][row][16 B] and scales [chunk][row][2 B] of a stage, chunk-major, before
+    they are dealt into the two halves of the stage image: packed codes uint8 [128, 128] (K = 256) +
+    scales uint8 [128, 16] -> uint8 [18432]."""
     codes = _codes(packed_rows).reshape(TILE_ROWS, CHUNKS, 2, 16)         # row, chunk, block, code
     sc = np.asarray(sf_rows, dtype=np.uint8).reshape(TILE_ROWS, CHUNKS, 2)
     mag = sc & 0x7F
@@ -198,9 +208,14 @@ def repack_matrix(packed: np.ndarray, sf: np.ndarray, pair_rows) -> np.ndarray:
         ra, rb = pair_rows(p)
         for s in range(stages):
             for t, r0 in enumerate((ra, rb)):
-                out[p, s, t * TILE_BYTES:(t + 1) * TILE_BYTES] = pack_tile_stage(
-                    packed[r0:r0 + TILE_ROWS, s * 128:(s + 1) * 128],
-                    sf[r0:r0 + TILE_ROWS, s * 16:(s + 1) * 16])
+                tile = pack_tile_stage(packed[r0:r0 + TILE_ROWS, s * 128:(s + 1) * 128],
+                                       sf[r0:r0 + TILE_ROWS, s * 16:(s + 1) * 16])
+                codes = tile[:TILE_CODE_BYTES].reshape(2, HALF_TILE_CODE_BYTES)        # chunks 0..3 | 4..7
+                scales = tile[TILE_CODE_BYTES:].reshape(2, TILE_SCALE_BYTES // 2)
+                for h in range(2):
+                    o = h * HALF_STAGE_BYTES + t * HALF_TILE_BYTES
+                    out[p, s, o:o + HALF_TILE_CODE_BYTES] = codes[h]
+                    out[p, s, o + HALF_TILE_CODE_BYTES:o + HALF_TILE_BYTES] = scales[h]
     return out
 
 

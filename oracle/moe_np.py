@@ -146,9 +146,10 @@ def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int 
       pos      int32 [T*k]           position of each route in ``sorted`` (-1 if not local)
       items    int32 [n_items, 3]    (local expert, first position, rows) work items: experts by
                                      load descending (ties by id), each cut into runs of <= chunk rows;
-                                     but when some expert has more than ``narrow`` rows, an expert with
-                                     at most 16 rows is one item and every other one is cut into runs of
-                                     <= wide rows
+                                     or ("wide step") an expert with at most 16 rows is one item and
+                                     every other one is cut into runs of <= wide rows: when some expert
+                                     has more than ``narrow`` rows and that cut has at least a tenth
+                                     fewer items
     """
     ids = np.asarray(ids, dtype=np.int64)
     flat = ids.reshape(-1)
@@ -165,8 +166,11 @@ def sort_routes(ids: np.ndarray, local_start: int, local_count: int, chunk: int 
     active = [e for e in np.argsort(-counts.astype(np.int64), kind="stable") if counts[e] > 0]
     items = []
     cmax = int(counts.max()) if counts.size else 0
+    n_narrow = sum(-(-int(counts[e]) // chunk) for e in active)
+    n_wide = sum(-(-int(counts[e]) // (16 if int(counts[e]) <= 16 else wide)) for e in active)
+    wide_step = cmax > narrow and 11 * n_wide <= 10 * n_narrow
     for e in active:
-        per = chunk if cmax <= narrow else (16 if int(counts[e]) <= 16 else wide)
+        per = chunk if not wide_step else (16 if int(counts[e]) <= 16 else wide)
         for c0 in range(0, int(counts[e]), per):
             items.append((int(e), int(offsets[e]) + c0, min(per, int(counts[e]) - c0)))
     return {"counts": counts, "offsets": offsets, "sorted": sorted_routes, "pos": pos,
