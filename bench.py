@@ -549,7 +549,10 @@ def measure(wl, tokens, args, dev, world, rank, *, state=None, layer=None, with_
             dist.barrier()
             out_rows = layer.step(h[t0:t1].contiguous(), lg[t0:t1].contiguous()).clone()
         torch.cuda.synchronize()
-        parity = _parity(wl, h, lg, out_rows, t0, state["ids"][:tokens], dev, n_tokens=4 if world == 1 else 2)
+        ids_step = state["ids"][:tokens]
+        if world > 1 and layer.route_in_gather:      # the router ran inside the gather kernel: its ids are in the exchange buffer
+            ids_step = layer.peer.routed_views(wl.top_k)[0]
+        parity = _parity(wl, h, lg, out_rows, t0, ids_step, dev, n_tokens=4 if world == 1 else 2)
         if world > 1:
             allp = [None] * world
             dist.all_gather_object(allp, parity)
@@ -636,12 +639,15 @@ def run_gpu(args):
             failed = failed or not a["parity"]["ok"]
         extra["sweep"] = rows
 
-    # kernels of this library per step beyond the single-GPU step's: the token push and, unless the
-    # combine is fused with the reduce-scatter, the pull-reduce (peer exchange); the cast (NCCL exchange)
+    # kernels of this library per step against the single-GPU step's five (top-k, sort, gather, GEMMs, combine).
+    # Peer exchange: + the token push, + the pull-reduce unless the combine is fused with the reduce-scatter,
+    # - top-k and sort when the router runs inside the push kernel.  NCCL exchange: + the cast.
     layer = m["layer"]
     ep_extra_launches = 0
     if world > 1:
-        ep_extra_launches = (1 if layer.fuse_combine else 2) if layer.exchange == "peer" else 1
+        ep_extra_launches = 1
+        if layer.exchange == "peer":
+            ep_extra_launches = (1 if layer.fuse_combine else 2) - (2 if layer.route_in_gather else 0)
     if rank == 0:
         line = {"metric": METRIC, "value": m["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": m["ms_per_step"], "higher_is_better": True,

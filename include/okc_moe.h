@@ -134,6 +134,21 @@ int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void
                     int T, const void* post_norm_w, void* workspace, void* out, int out_f32,
                     okc_stream_t stream);
 
+/*
+ * okc_moe_experts with the pre-expert RMSNorm of the reference's decode layer applied while the token
+ * rows are gathered: a row x becomes bf16(x * rsqrt(mean(x^2) + pre_eps) * pre_gain[k]) before the gate_up
+ * GEMM (the layer passes pre_gain = 1 + pre_expert_norm, eps 1e-5).  hidden: bf16 rows, or with
+ * hidden_f32 != 0 f32 rows, which are rounded to bf16 first as the reference does (the pooler's FP32
+ * output goes in without a round trip); hidden_stride in elements of that type.  pre_gain: f32 [H],
+ * H <= 8192.  Together with out_f32 = 1 (FP32 rows for the unpooler) these are the steps either side of
+ * the MoE block in the layer.  Replaces `moe_gathern_launch` (muse_decode_layer/layer.py:1700-1745).
+ */
+int okc_moe_experts_prenorm(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
+                            const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,
+                            int hidden_f32, const float* pre_gain, float pre_eps, int T,
+                            const void* post_norm_w, void* workspace, void* out, int out_f32,
+                            okc_stream_t stream);
+
 /* okc_moe_experts with CUDA events around its three kernels: synchronises, then writes their
  * durations in milliseconds to the host array phase_ms[4] = {gather, grouped GEMMs (gate_up and
  * down units in one launch), combine, whole call}.
@@ -233,6 +248,17 @@ int okc_moe_experts_ep(const okc_moe_plan* plan, const void* packed_w13, const v
                        const float* gs13, const float* gs2, const void* hidden, int64_t hidden_stride,
                        int T, void* workspace, const okc_ep_comm* comm, void* out_bf16,
                        okc_stream_t stream);
+/* okc_ep_gather_tokens with the router in it, in one kernel: the rank routes its own token block (softmax
+ * top-k, as okc_moe_route) while it stores the rows into every rank's buffer, sends the k ids and weights of
+ * each token instead of its logits (they take the place of the logits in the buffer: ids int32 [T, top_k],
+ * then weights f32 [T, top_k]; okc_ep_routed_views gives their addresses; needs 2 * top_k <= n_experts), and
+ * once every rank's flag has been seen sorts the routes of the whole step into `workspace` as okc_moe_sort
+ * does, the shared expert on the rank's own token block.  The caller goes on with okc_moe_experts_ep (or
+ * okc_moe_experts + okc_ep_reduce_scatter).  Three launches fewer than gather + route.  No counterpart in the
+ * reference. */
+int okc_ep_route_gather(const okc_moe_plan* plan, const okc_ep_comm* comm, const void* hidden_own,
+                        int64_t hidden_stride, const float* logits_own, void* workspace, okc_stream_t stream);
+int okc_ep_routed_views(const okc_ep_comm* comm, int top_k, void** ids_all, void** weights_all);
 /* Raises, in this rank's own buffer, the flag that rank `from_rank` raises when its token rows
  * (which = 0) or its partial sums (which = 1) of the coming exchange are in place.  For a harness that
  * runs the ranks of a step one after the other on one device (there the later rank's data is put in

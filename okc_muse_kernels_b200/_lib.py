@@ -63,6 +63,8 @@ SIGNATURES = {
     "okc_moe_route_hidden": (C.c_int, [_PLAN, C.POINTER(Router), _P, C.c_int64, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
     "okc_moe_sort": (C.c_int, [_PLAN, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "okc_moe_experts": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P]),
+    "okc_moe_experts_prenorm": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, C.c_float, C.c_int, _P, _P, _P,
+                                          C.c_int, _P]),
     "okc_moe_experts_profiled": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P,
                                            C.POINTER(C.c_float)]),
     "okc_moe_cast_bf16": (C.c_int, [_P, _P, C.c_int64, _P]),
@@ -80,6 +82,8 @@ SIGNATURES = {
     "okc_ep_gather_tokens": (C.c_int, [_COMM, _P, C.c_int64, _P, _P]),
     "okc_ep_reduce_scatter": (C.c_int, [_COMM, _P, _P]),
     "okc_moe_experts_ep": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _COMM, _P, _P]),
+    "okc_ep_route_gather": (C.c_int, [_PLAN, _COMM, _P, C.c_int64, _P, _P, _P]),
+    "okc_ep_routed_views": (C.c_int, [_COMM, C.c_int, C.POINTER(_P), C.POINTER(_P)]),
     "okc_ep_mark_arrived": (C.c_int, [_COMM, C.c_int, C.c_int, _P]),
     "okc_ep_read_status": (C.c_int, [_COMM, _P, C.POINTER(C.c_int32)]),
 }

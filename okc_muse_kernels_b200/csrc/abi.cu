@@ -86,6 +86,18 @@ static Ws carve(void* workspace, const Geometry& g) {
   return w;
 }
 
+// The fields of RouteParams that follow from the plan and the workspace (sources and sinks of ids / weights / logits are left null).
+static void fill_route_params(const okc_moe_plan* plan, const Geometry& g, int T, int own_t0, int own_t1, void* workspace,
+                              RouteParams& p) {
+  Ws w = carve(workspace, g);
+  memset(&p, 0, sizeof(p));
+  p.meta = w.meta; p.counts = w.counts; p.items = w.items; p.sorted = w.sorted; p.pos = w.pos; p.wsorted = w.wsorted;
+  p.T = T; p.E = plan->n_experts; p.k = plan->top_k; p.kk = g.kk; p.slots = g.slots;
+  p.local_start = plan->local_start; p.local_count = plan->local_count; p.has_shared = plan->shared_inter ? 1 : 0;
+  p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items; p.chunk_rows = chunk_rows_for(T, plan->top_k, plan->n_experts);
+  p.router_mode = 0; p.router_mult = 1.0f; p.H = g.H;
+}
+
 static int route_common(const okc_moe_plan* plan, const float* logits, const int32_t* ids_in, const float* wts_in,
                         int T, int own_t0, int own_t1, int32_t* ids_out, float* wts_out, void* workspace,
                         cudaStream_t stream, const okc_router* router = nullptr, const void* hidden = nullptr,
@@ -94,15 +106,9 @@ static int route_common(const okc_moe_plan* plan, const float* logits, const int
   if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
   if (!workspace || !aligned(workspace, 256) || T <= 0 || T > plan->max_tokens) return OKC_ERR_BAD_ARG;
   if (own_t0 < 0 || own_t1 < own_t0 || own_t1 > T) return OKC_ERR_BAD_ARG;
-  Ws w = carve(workspace, g);
   RouteParams p;
+  fill_route_params(plan, g, T, own_t0, own_t1, workspace, p);
   p.logits = logits; p.ids_in = ids_in; p.wts_in = wts_in; p.ids_out = ids_out; p.wts_out = wts_out;
-  p.meta = w.meta; p.counts = w.counts; p.items = w.items; p.sorted = w.sorted; p.pos = w.pos; p.wsorted = w.wsorted;
-  p.T = T; p.E = plan->n_experts; p.k = plan->top_k; p.kk = g.kk; p.slots = g.slots;
-  p.local_start = plan->local_start; p.local_count = plan->local_count; p.has_shared = plan->shared_inter ? 1 : 0;
-  p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items; p.chunk_rows = chunk_rows_for(T, plan->top_k, plan->n_experts);
-  p.router_mode = 0; p.router_mult = 1.0f; p.router_bias = nullptr; p.router_w = nullptr; p.hidden = nullptr;
-  p.hidden_stride = 0; p.H = g.H; p.router_splits = 0; p.router_part = nullptr;
   if (router) {
     if (router->mode != 0 && router->mode != 1) return OKC_ERR_BAD_ARG;
     p.router_mode = router->mode; p.router_mult = router->multiplier; p.router_bias = router->bias;
@@ -118,7 +124,7 @@ static int route_common(const okc_moe_plan* plan, const float* logits, const int
       if (splits > 16) splits = 16;
       if (splits < 1) return OKC_ERR_BAD_PLAN;
       p.router_w = router->w; p.hidden = static_cast<const uint16_t*>(hidden); p.hidden_stride = hidden_stride;
-      p.router_splits = static_cast<int>(splits); p.router_part = w.y;
+      p.router_splits = static_cast<int>(splits); p.router_part = carve(workspace, g).y;
     }
   }
   return launch_route(p, stream) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
@@ -224,14 +230,23 @@ int okc_moe_route_hidden(const okc_moe_plan* plan, const okc_router* router, con
 // before / between / after them (gather, gate_up, down, combine).
 static bool ep_params(const okc_ep_comm* c, EpParams& p);
 
+// Optional pre-expert norm of the token rows, applied by the gather.
+struct PreNorm {
+  const float* gain;   // f32 [H]
+  float eps;
+  int hidden_f32;      // the token rows are f32 (rounded to bf16 first) instead of bf16
+};
+
 static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
                         const float* gs2, const void* hidden, int64_t hidden_stride, int T, const void* post_norm_w,
                         void* workspace, void* out, int out_f32, cudaStream_t stream, cudaEvent_t* ev,
-                        const EpParams* ep = nullptr) {
+                        const EpParams* ep = nullptr, const PreNorm* pre = nullptr) {
   Geometry g;
   if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
   if (!packed_w13 || !packed_w2 || !gs13 || !gs2 || !hidden || !workspace || !out) return OKC_ERR_BAD_ARG;
-  if (T <= 0 || T > plan->max_tokens || hidden_stride < g.H || (hidden_stride % 8) != 0) return OKC_ERR_BAD_ARG;
+  const bool f32_rows = pre != nullptr && pre->hidden_f32 != 0;
+  if (T <= 0 || T > plan->max_tokens || hidden_stride < g.H || (hidden_stride % (f32_rows ? 4 : 8)) != 0) return OKC_ERR_BAD_ARG;
+  if (pre && (!pre->gain || !aligned(pre->gain, 16) || !(pre->eps >= 0.0f) || g.H > 8192)) return OKC_ERR_BAD_ARG;
   if (!aligned(packed_w13, 16) || !aligned(packed_w2, 16) || !aligned(hidden, 16) || !aligned(workspace, 256) ||
       !aligned(out, 16))
     return OKC_ERR_BAD_ARG;
@@ -244,8 +259,10 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   const int R = T * g.kk;
 
   if (ev && cudaEventRecord(ev[0], stream) != cudaSuccess) return OKC_ERR_CUDA;
-  if (launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, w.done, g.max_items, stream) != cudaSuccess)
-    return OKC_ERR_CUDA;
+  const cudaError_t ge = pre ? launch_gather_norm(hidden, hidden_stride, pre->hidden_f32, pre->gain, pre->eps, w.meta, w.sorted,
+                                                  g.kk, g.H, R, w.xg, w.done, g.max_items, stream)
+                             : launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, w.done, g.max_items, stream);
+  if (ge != cudaSuccess) return OKC_ERR_CUDA;
   if (ev && cudaEventRecord(ev[1], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
   // Both GEMM phases in one persistent launch: gate_up units first, then down units, each down
@@ -286,6 +303,17 @@ int okc_moe_experts(const okc_moe_plan* plan, const void* packed_w13, const void
                     void* workspace, void* out, int out_f32, okc_stream_t stream) {
   return experts_impl(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, T, post_norm_w, workspace, out,
                       out_f32, reinterpret_cast<cudaStream_t>(stream), nullptr);
+}
+
+int okc_moe_experts_prenorm(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2, const float* gs13,
+                            const float* gs2, const void* hidden, int64_t hidden_stride, int hidden_f32,
+                            const float* pre_gain, float pre_eps, int T, const void* post_norm_w, void* workspace,
+                            void* out, int out_f32, okc_stream_t stream) {
+  PreNorm pre;
+  pre.gain = pre_gain; pre.eps = pre_eps; pre.hidden_f32 = hidden_f32 ? 1 : 0;
+  if (!pre_gain) return OKC_ERR_BAD_ARG;
+  return experts_impl(plan, packed_w13, packed_w2, gs13, gs2, hidden, hidden_stride, T, post_norm_w, workspace, out,
+                      out_f32, reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, &pre);
 }
 
 int okc_moe_experts_profiled(const okc_moe_plan* plan, const void* packed_w13, const void* packed_w2,
@@ -417,6 +445,36 @@ int okc_ep_reduce_scatter(const okc_ep_comm* comm, void* out_bf16, okc_stream_t 
   if (!out_bf16 || !aligned(out_bf16, 8)) return OKC_ERR_BAD_ARG;
   p.out = static_cast<uint16_t*>(out_bf16);
   return launch_ep_reduce(p, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
+}
+
+int okc_ep_routed_views(const okc_ep_comm* comm, int top_k, void** ids_all, void** weights_all) {
+  EpParams p;
+  if (!ep_params(comm, p) || top_k <= 0 || 2 * top_k > p.E) return OKC_ERR_BAD_ARG;
+  uint8_t* mine = p.peer[p.rank];
+  if (ids_all) *ids_all = mine + p.off_logits;
+  if (weights_all) *weights_all = mine + p.off_logits + static_cast<size_t>(p.tokens) * top_k * 4;
+  return OKC_OK;
+}
+
+int okc_ep_route_gather(const okc_moe_plan* plan, const okc_ep_comm* comm, const void* hidden_own, int64_t hidden_stride,
+                        const float* logits_own, void* workspace, okc_stream_t stream) {
+  EpParams p;
+  if (!ep_params(comm, p)) return OKC_ERR_BAD_ARG;
+  Geometry g;
+  if (!plan || !make_geometry(*plan, g)) return OKC_ERR_BAD_PLAN;
+  if (plan->n_experts != p.E || plan->hidden != p.H || 2 * plan->top_k > p.E || p.tokens > plan->max_tokens) return OKC_ERR_BAD_PLAN;
+  if (!hidden_own || !logits_own || !workspace || !aligned(hidden_own, 16) || !aligned(logits_own, 16) || !aligned(workspace, 256))
+    return OKC_ERR_BAD_ARG;
+  if (hidden_stride < p.H || (hidden_stride % 8) != 0) return OKC_ERR_BAD_ARG;
+  if (!is_sm100()) return OKC_ERR_NO_DEVICE;
+  p.hidden_own = static_cast<const uint16_t*>(hidden_own); p.hidden_stride = hidden_stride; p.logits_own = logits_own;
+  const int tb = p.tokens / p.world;
+  RouteParams rp;
+  fill_route_params(plan, g, p.tokens, p.rank * tb, (p.rank + 1) * tb, workspace, rp);
+  uint8_t* mine = p.peer[p.rank];
+  rp.ids_in = reinterpret_cast<const int32_t*>(mine + p.off_logits);
+  rp.wts_in = reinterpret_cast<const float*>(mine + p.off_logits + static_cast<size_t>(p.tokens) * plan->top_k * 4);
+  return launch_ep_push_route_sort(p, rp, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? OKC_OK : OKC_ERR_CUDA;
 }
 
 int okc_ep_mark_arrived(const okc_ep_comm* comm, int which, int from_rank, okc_stream_t stream) {

@@ -11,6 +11,10 @@
 //                 reduce-scatter and the cast in one kernel.
 //   combine_reduce: the per-token combine of the local experts' outputs and pull_reduce in one
 //                 kernel (the partial sums of a rank's own rows never leave its registers).
+//   push_route_sort: push_tokens with the router in it: a rank routes its own tokens (top-k) while it
+//                 stores their rows, sends the ids and weights instead of the logits, and the CTA that
+//                 has seen every rank's flag sorts the routes of the whole step: three launches and
+//                 their gaps fewer on the way to the first GEMM unit.
 //
 // The reference has no counterpart: its expert all-reduce is not run (muse_moe_w4a16/baseline.py:8).
 //
@@ -30,7 +34,7 @@
 #include <cstdint>
 
 #include "../../include/okc_moe.h"
-#include "params.cuh"
+#include "route_device.cuh"
 
 namespace okc {
 
@@ -245,6 +249,86 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
       ctrl[kEpCtrlSeqRs] = seq;
     }
   }
+}
+
+// push_tokens + top-k of the rank's own tokens + the token -> expert sort of the whole step.
+// grid (row groups, world), 256 threads, dynamic shared memory of route_smem_bytes(R, slots, 256) bytes.
+// CTA (x, r): for rows x, x + gridDim.x, ... of this rank's block, warp 0 routes the row and stores its k
+// ids and weights into rank r's buffer (the logits area of the buffer holds ids int32 [T, k], then weights
+// f32 [T, k]), all warps store the row itself.  The last CTA to finish raises the flags, waits for every
+// rank's, and sorts.
+template <int PER>
+__global__ void __launch_bounds__(256) okc_ep_push_route_sort(const EpParams p, const RouteParams rp) {
+  extern __shared__ int32_t sm[];
+  griddep_wait();
+  griddep_launch_dependents();   // the gather kernel may set itself up; it waits for this grid to complete
+  uint8_t* mine = p.peer[p.rank];
+  uint8_t* dest = p.peer[blockIdx.y];
+  const int tb = p.tokens / p.world;
+  const int hv = p.H / 8;        // 16-byte vectors per hidden row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k = rp.k;
+  for (int row = blockIdx.x; row < tb; row += gridDim.x) {
+    const size_t t = static_cast<size_t>(p.rank) * tb + row;
+    if (warp == 0) {
+      int32_t* ids_d = reinterpret_cast<int32_t*>(dest + p.off_logits) + t * k;
+      float* wts_d = reinterpret_cast<float*>(dest + p.off_logits + static_cast<size_t>(p.tokens) * k * 4) + t * k;
+      topk_token<PER>(p.logits_own + static_cast<size_t>(row) * p.E, 1, 0, p.E, k, 0, 1.0f, nullptr, lane, ids_d, wts_d);
+    }
+    const uint4* hs = reinterpret_cast<const uint4*>(p.hidden_own + static_cast<size_t>(row) * p.hidden_stride);
+    uint4* hd = reinterpret_cast<uint4*>(dest + p.off_hidden) + t * hv;
+    for (int i = threadIdx.x; i < hv; i += blockDim.x) hd[i] = hs[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  int32_t* ctrl = ctrl_of(mine);
+  if (threadIdx.x == 0) {
+    const int total = gridDim.x * gridDim.y;
+    s_last = (atomicAdd(&ctrl[kEpCtrlDoneIn], 1) == total - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // every CTA of this rank has stored (and fenced) its rows: tell everybody, then wait for everybody
+  __threadfence_system();
+  const int32_t seq = ctrl[kEpCtrlSeqIn] + 1;
+  if (threadIdx.x < p.world) {
+    st_release_sys(flags_in_of(p.peer[threadIdx.x]) + p.rank, seq);
+    if (!wait_flag(flags_in_of(mine) + threadIdx.x, seq, p.wait_ns)) {
+      atomicCAS(&ctrl[kEpCtrlStatus], 0, OKC_ERR_TIMEOUT);
+      atomicCAS(&ctrl[kEpCtrlDetail], 0, 0x100 | threadIdx.x);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ctrl[kEpCtrlDoneIn] = 0;
+    ctrl[kEpCtrlSeqIn] = seq;
+  }
+  // the ids and weights of all tokens are in this rank's buffer now
+  sort_routes_cta<256>(rp, sm);
+}
+
+cudaError_t launch_ep_push_route_sort(const EpParams& p, const RouteParams& rp, cudaStream_t stream) {
+  const int tb = p.tokens / p.world;
+  int gx = 128 / p.world;
+  if (gx < 1) gx = 1;
+  if (gx > tb) gx = tb;
+  const size_t smem = route_smem_bytes(rp.T * rp.kk, rp.slots, 256);
+  const dim3 grid(gx, p.world), block(256);
+  cudaError_t e;
+  if (p.E <= 128) {
+    e = cudaFuncSetAttribute(okc_ep_push_route_sort<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    return launch_kernel(okc_ep_push_route_sort<4>, grid, block, smem, stream, true, p, rp);
+  }
+  if (p.E <= 256) {
+    e = cudaFuncSetAttribute(okc_ep_push_route_sort<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    return launch_kernel(okc_ep_push_route_sort<8>, grid, block, smem, stream, true, p, rp);
+  }
+  e = cudaFuncSetAttribute(okc_ep_push_route_sort<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  return launch_kernel(okc_ep_push_route_sort<16>, grid, block, smem, stream, true, p, rp);
 }
 
 // One thread: the flag rank `from` raises on this rank when its part of the coming exchange is in

@@ -34,6 +34,10 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
 cudaError_t launch_gather(const void* hidden, int64_t stride, int32_t* meta, const int32_t* sorted, int kk,
                           int H, int R, void* xg, int32_t* done, int max_items, cudaStream_t stream);
 
+cudaError_t launch_gather_norm(const void* hidden, int64_t stride, int hidden_f32, const float* gain, float eps,
+                               int32_t* meta, const int32_t* sorted, int kk, int H, int R, void* xg, int32_t* done,
+                               int max_items, cudaStream_t stream);
+
 struct RepackParams {
   const uint8_t* w;
   const uint8_t* sf;
@@ -92,6 +96,7 @@ struct EpParams {
 };
 cudaError_t launch_ep_push(const EpParams& p, cudaStream_t stream);
 cudaError_t launch_ep_reduce(const EpParams& p, cudaStream_t stream);
+cudaError_t launch_ep_push_route_sort(const EpParams& p, const RouteParams& rp, cudaStream_t stream);
 cudaError_t launch_ep_mark_arrived(const EpParams& p, int which, int from, cudaStream_t stream);
 
 struct CombineParams {
@@ -107,7 +112,6 @@ cudaError_t launch_ep_combine_reduce(const EpParams& p, const CombineParams& c, 
 
 cudaError_t launch_cast(const float* in, void* out_bf16, int64_t n, cudaStream_t stream);
 cudaError_t launch_wait_timeout_probe(int32_t* status, cudaStream_t stream);
-size_t route_smem_bytes(int R, int slots);
 
 // Launch with (pdl = true) or without the programmatic-serialization attribute.
 template <typename... KArgs, typename... Args>

@@ -6,31 +6,20 @@
 //   * stable (expert, route index) order        muse_moe_w4a16/submission.py:2236-2328 (moe_routegather)
 //   * active experts by load, heaviest first    muse_moe_w4a16/submission.py:345-350
 // The order inside an expert is deterministic (the reference's moe_route fills it with atomics).
-#include "params.cuh"
+#include <cuda_bf16.h>
+
+#include "route_device.cuh"
 
 namespace okc {
 
 
 constexpr int kRouteThreads = 1024;
-constexpr int kRouteWarps = kRouteThreads / 32;
 
-// Optional phase clock of the route kernel (-DOKC_WAIT_PROFILE): thread 0's clock at each phase end.
 #ifdef OKC_WAIT_PROFILE
-__device__ long long g_route_prof[8];
-#define OKC_ROUTE_MARK(i) { if (threadIdx.x == 0) g_route_prof[i] = clock64(); }
 extern "C" int okc_moe_debug_route_profile(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, g_route_prof, sizeof(g_route_prof)) == cudaSuccess ? 0 : -3;
 }
-#else
-#define OKC_ROUTE_MARK(i)
 #endif
-
-__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
-
-__device__ __forceinline__ int items_of(int c, bool wide_step, int chunk) {
-  const int per = item_rows(c, wide_step, chunk);
-  return (c + per - 1) / per;
-}
 
 // Router logits from the token rows: part[ks][t][e] = sum over the K range of split ks of
 // hidden[t][k] * w[e][k], FP32 multiply-adds in ascending k (bf16 -> f32 is exact).  The step before
@@ -131,257 +120,14 @@ __global__ void __launch_bounds__(256) okc_route_topk(const float* __restrict__ 
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
-  float v[PER];    // selection keys
-  float sc[PER];   // what the weights are made of (mode 1: the unbiased scores)
-#pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    const int e = lane + 32 * j;
-    float x = -INFINITY;
-    if (e < E) {
-      x = logits[static_cast<size_t>(t) * E + e];
-      for (int s = 1; s < n_part; ++s) x += logits[(static_cast<size_t>(s) * T + t) * E + e];
-    }
-    if (mode == 1 && e < E) {
-      const float s1 = 1.0f / (1.0f + expf(-x * mult));
-      sc[j] = s1;
-      x = s1 + (bias != nullptr ? bias[e] : 0.f);
-    } else {
-      sc[j] = x;
-    }
-    v[j] = (x == x) ? x : -INFINITY;
-  }
-  uint32_t taken = 0;
-  float bv = -INFINITY, bs = 0.f;
-  int bi = 0x7fffffff;
-#pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    const int e = lane + 32 * j;
-    if (e < E && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; bs = sc[j]; }
-  }
-  float my_val = 0.f;
-  int my_id = 0;
-  for (int r = 0; r < k; ++r) {
-    float wv = bv, wsc = bs;
-    int wi = bi;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
-      const float os = __shfl_xor_sync(0xffffffffu, wsc, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
-      if (better(ov, oi, wv, wi)) { wv = ov; wi = oi; wsc = os; }
-    }
-    if (lane == r) { my_val = wsc; my_id = wi; }
-    if (wi == bi) {
-      // this lane held the winner: next best of what it has left
-      taken |= 1u << (wi >> 5);
-      bv = -INFINITY;
-      bs = 0.f;
-      bi = 0x7fffffff;
-#pragma unroll
-      for (int j = 0; j < PER; ++j) {
-        const int e = lane + 32 * j;
-        if (e < E && !((taken >> j) & 1u) && better(v[j], e, bv, bi)) { bv = v[j]; bi = e; bs = sc[j]; }
-      }
-    }
-  }
-  float ex;
-  if (mode == 1) {
-    ex = (lane < k) ? my_val : 0.f;
-  } else {
-    const float top = __shfl_sync(0xffffffffu, my_val, 0);
-    ex = (lane < k) ? expf(my_val - top) : 0.f;
-  }
-  float sum = ex;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if (lane < k) {
-    ids_out[t * k + lane] = my_id;
-    wts_out[t * k + lane] = (mode == 1) ? ex / (sum + 1e-15f) : ex / sum;
-  }
+  topk_token<PER>(logits + static_cast<size_t>(t) * E, n_part, static_cast<size_t>(T) * E, E, k, mode, mult, bias, lane,
+                  ids_out + t * k, wts_out + t * k);
 }
 
 __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RouteParams p) {
   extern __shared__ int32_t sm[];
-  const int R = p.T * p.kk;
-  // shared memory: rexp int32 [R] (local expert slot or -1) | whist int32 [32][slots] | order int32 [slots]
-  // | cnt int32 [slots+1] | offs int32 [slots+1] | ibase int32 [slots+1]
-  int32_t* rexp = sm;
-  int32_t* whist = rexp + R;
-  int32_t* order = whist + kRouteWarps * p.slots;
-  int32_t* cnt = order + p.slots;
-  int32_t* offs = cnt + p.slots + 1;
-  int32_t* ibase = offs + p.slots + 1;
-  __shared__ int s_nact;
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) s_nact = 0;
   griddep_wait();   // the ids may come from the top-k kernel launched just before
-  OKC_ROUTE_MARK(0)
-
-  for (int i = tid; i < kRouteWarps * p.slots; i += kRouteThreads) whist[i] = 0;
-  for (int i = tid; i < R; i += kRouteThreads) p.sorted[i] = -1;
-
-  // ---- 1. the routes' expert slots (global ids outside the local range are skipped)
-  for (int i = tid; i < p.T * p.k; i += kRouteThreads) {
-    const int t = i / p.k, sl = i - t * p.k;
-    const int le = p.ids_in[i] - p.local_start;
-    rexp[t * p.kk + sl] = (le >= 0 && le < p.local_count) ? le : -1;
-  }
-  if (p.has_shared)
-    for (int t = tid; t < p.T; t += kRouteThreads)
-      rexp[t * p.kk + p.k] = (t >= p.own_t0 && t < p.own_t1) ? p.local_count : -1;
-  __syncthreads();
-  OKC_ROUTE_MARK(1)
-
-  // ---- 2. per-warp histograms over contiguous chunks of the route list
-  const int chunk = ((R + kRouteWarps - 1) / kRouteWarps + 31) & ~31;
-  const int r0 = warp * chunk;
-  for (int b = 0; b < chunk; b += 32) {
-    const int i = r0 + b + lane;
-    const int e = (i < R) ? rexp[i] : -1;
-    const uint32_t m = __match_any_sync(0xffffffffu, e);
-    if (e >= 0 && lane == (__ffs(m) - 1)) whist[warp * p.slots + e] += __popc(m);
-    __syncwarp();
-  }
-  __syncthreads();
-  // exclusive prefix over warps per expert slot
-  for (int e = tid; e < p.slots; e += kRouteThreads) {
-    int run = 0;
-    for (int w = 0; w < kRouteWarps; ++w) {
-      const int c = whist[w * p.slots + e];
-      whist[w * p.slots + e] = run;
-      run += c;
-    }
-    cnt[e] = run;
-    p.counts[e] = run;
-  }
-  __syncthreads();
-  OKC_ROUTE_MARK(2)
-  // ---- 3. offsets (exclusive scan over slots) by warp 0
-  if (warp == 0) {
-    const int per = (p.slots + 31) >> 5;
-    int local = 0;
-    for (int j = 0; j < per; ++j) {
-      const int e = lane * per + j;
-      if (e < p.slots) local += cnt[e];
-    }
-    int incl = local;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
-    }
-    int run = incl - local;
-    for (int j = 0; j < per; ++j) {
-      const int e = lane * per + j;
-      if (e < p.slots) { offs[e] = run; run += cnt[e]; }
-    }
-    if (lane == 31) { offs[p.slots] = incl; p.counts[p.slots] = incl; }
-  }
-  __syncthreads();
-
-  OKC_ROUTE_MARK(3)
-  // ---- 4. stable positions: offset of the expert + routes of that expert before this one
-  for (int b = 0; b < chunk; b += 32) {
-    const int i = r0 + b + lane;
-    const int e = (i < R) ? rexp[i] : -1;
-    const uint32_t m = __match_any_sync(0xffffffffu, e);
-    if (i < R) {
-      if (e >= 0) {
-        const int q = offs[e] + whist[warp * p.slots + e] + __popc(m & ((1u << lane) - 1u));
-        const int t = i / p.kk, s = i - t * p.kk;
-        float w = 1.0f;
-        if (s < p.k) w = p.wts_in[t * p.k + s];
-        p.pos[i] = q;
-        p.sorted[q] = i;
-        p.wsorted[q] = w;
-      } else {
-        p.pos[i] = -1;
-      }
-    }
-    __syncwarp();
-    if (e >= 0 && lane == (31 - __clz(m))) whist[warp * p.slots + e] += __popc(m);
-    __syncwarp();
-  }
-
-  OKC_ROUTE_MARK(4)
-  // ---- 5. work items: experts by load descending (ties by id), cut into runs of item_rows() rows
-  int active = 0;
-  for (int e = tid; e < p.slots; e += kRouteThreads) {
-    const int c = cnt[e];
-    if (c > 0) {
-      int rank = 0;
-      for (int o = 0; o < p.slots; ++o) {
-        const int co = cnt[o];
-        rank += (co > c || (co == c && o < e)) ? 1 : 0;
-      }
-      order[rank] = e;
-      ++active;
-    }
-  }
-  if (active) atomicAdd(&s_nact, active);
-  __syncthreads();
-  OKC_ROUTE_MARK(5)
-  const int n_active = s_nact;
-  __shared__ int s_wide;
-  if (warp == 0) {
-    const int per = (n_active + 31) >> 5;
-    // narrow or wide step: the item counts of both cuts decide (the heaviest expert is order[0])
-    int n_narrow = 0, n_wide = 0;
-    for (int j = 0; j < per; ++j) {
-      const int r = lane * per + j;
-      if (r < n_active) {
-        n_narrow += items_of(cnt[order[r]], false, p.chunk_rows);
-        n_wide += items_of(cnt[order[r]], true, p.chunk_rows);
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      n_narrow += __shfl_xor_sync(0xffffffffu, n_narrow, o);
-      n_wide += __shfl_xor_sync(0xffffffffu, n_wide, o);
-    }
-    const int cmax = n_active > 0 ? cnt[order[0]] : 0;
-    const bool wide_step = wide_step_pays(cmax, n_narrow, n_wide);
-    int local = 0;
-    for (int j = 0; j < per; ++j) {
-      const int r = lane * per + j;
-      if (r < n_active) local += items_of(cnt[order[r]], wide_step, p.chunk_rows);
-    }
-    int incl = local;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
-    }
-    int run = incl - local;
-    for (int j = 0; j < per; ++j) {
-      const int r = lane * per + j;
-      if (r < n_active) { ibase[r] = run; run += items_of(cnt[order[r]], wide_step, p.chunk_rows); }
-    }
-    if (lane == 31) {
-      s_wide = wide_step ? 1 : 0;
-      p.meta[kMetaItems] = incl < p.max_items ? incl : p.max_items;
-      p.meta[kMetaLocalRoutes] = offs[p.slots];
-      p.meta[kMetaStatus] = 0;
-      p.meta[kMetaDetail] = 0;
-      p.meta[kMetaTokens] = p.T;
-      // the widest item is the first one of the heaviest expert
-      p.meta[kMetaWcap] = item_pad(min(cmax, item_rows(cmax, wide_step, p.chunk_rows)));
-    }
-  }
-  __syncthreads();
-  const bool wide_step = s_wide != 0;
-  for (int r = tid; r < n_active; r += kRouteThreads) {
-    const int e = order[r];
-    const int c = cnt[e];
-    int it = ibase[r];
-    const int per = item_rows(c, wide_step, p.chunk_rows);
-    for (int c0 = 0; c0 < c && it < p.max_items; c0 += per, ++it) {
-      const int n = min(per, c - c0);
-      p.items[it] = make_int4(e, offs[e] + c0, n, item_pad(n));
-    }
-  }
-  OKC_ROUTE_MARK(6)
+  sort_routes_cta<kRouteThreads>(p, sm);
 }
 
 // xg[pos] = hidden[token of the route at pos]: rows of the gate_up GEMM's token operand in expert order.
@@ -404,6 +150,82 @@ __global__ void __launch_bounds__(128) okc_gather_rows(const uint16_t* __restric
   const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * stride);
   uint4* dst = reinterpret_cast<uint4*>(xg + static_cast<size_t>(q) * H);
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// The same gather with the pre-expert RMSNorm of the reference's layer applied on the way
+// (muse_decode_layer/layer.py:1700-1745 `moe_gathern`; reference.py:465): the token row, FP32 rows
+// rounded to bf16 first, becomes bf16(x * rsqrt(mean(x^2) + eps) * gain[k]).  One CTA per sorted position,
+// the row held in registers between the sum of squares and the scaling (H <= 8192).
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 4;    // 16-byte vectors of 8 bf16 per thread: H <= 256 * 4 * 8
+template <bool F32>
+__global__ void __launch_bounds__(kNormThreads) okc_gather_rows_norm(const void* __restrict__ hidden, int64_t stride,
+                                                                    const float* __restrict__ gain, float eps,
+                                                                    int32_t* __restrict__ meta,
+                                                                    const int32_t* __restrict__ sorted, int kk, int H,
+                                                                    uint16_t* __restrict__ xg, int32_t* __restrict__ done,
+                                                                    int max_items) {
+  griddep_wait();
+  griddep_launch_dependents();
+  const int q = blockIdx.x, tid = threadIdx.x;
+  if (q == 0) {
+    for (int i = tid; i < max_items; i += blockDim.x) done[i] = 0;
+    if (tid < 3) meta[kMetaWorkFused + tid] = 0;
+  }
+  if (q >= meta[kMetaLocalRoutes]) return;
+  const int t = sorted[q] / kk;
+  const int nvec = H / 8;
+  float v[kNormMaxVec][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int o = tid + kNormThreads * i;
+    if (o < nvec) {
+      if (F32) {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(hidden) + static_cast<size_t>(t) * stride) + 2 * o;
+        const float4 a = src[0], b = src[1];
+        const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16_rn(f[j]));
+      } else {
+        const uint4 u = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(hidden) + static_cast<size_t>(t) * stride)[o];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[i][2 * j] = __uint_as_float(w[j] << 16);
+          v[i][2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+    }
+  }
+  __shared__ float red[kNormThreads / 32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
+  const float r = rsqrtf(tot / static_cast<float>(H) + eps);
+  uint4* dst = reinterpret_cast<uint4*>(xg + static_cast<size_t>(q) * H);
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int o = tid + kNormThreads * i;
+    if (o < nvec) {
+      const float4 g0 = reinterpret_cast<const float4*>(gain)[2 * o], g1 = reinterpret_cast<const float4*>(gain)[2 * o + 1];
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(v[i][2 * j] * r * g[2 * j]));
+        const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(v[i][2 * j + 1] * r * g[2 * j + 1]));
+        w[j] = lo | (hi << 16);
+      }
+      dst[o] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
 }
 
 // Exercises the bounded wait on purpose: one warp waits on an mbarrier that nothing ever arrives
@@ -431,12 +253,9 @@ cudaError_t launch_wait_timeout_probe(int32_t* status, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-size_t route_smem_bytes(int R, int slots) {
-  return sizeof(int32_t) * (static_cast<size_t>(R) + kRouteWarps * slots + slots + 3 * (slots + 1));
-}
 
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
-  const size_t smem = route_smem_bytes(p.T * p.kk, p.slots);
+  const size_t smem = route_smem_bytes(p.T * p.kk, p.slots, kRouteThreads);
   cudaError_t e = cudaFuncSetAttribute(okc_route_sort, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   if (p.logits != nullptr || p.router_w != nullptr) {
@@ -472,6 +291,16 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
     return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, q);
   }
   return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, p);
+}
+
+cudaError_t launch_gather_norm(const void* hidden, int64_t stride, int hidden_f32, const float* gain, float eps,
+                               int32_t* meta, const int32_t* sorted, int kk, int H, int R, void* xg, int32_t* done,
+                               int max_items, cudaStream_t stream) {
+  if (hidden_f32)
+    return launch_kernel(okc_gather_rows_norm<true>, dim3(R), dim3(kNormThreads), 0, stream, true, hidden, stride, gain, eps,
+                         meta, sorted, kk, H, static_cast<uint16_t*>(xg), done, max_items);
+  return launch_kernel(okc_gather_rows_norm<false>, dim3(R), dim3(kNormThreads), 0, stream, true, hidden, stride, gain, eps,
+                       meta, sorted, kk, H, static_cast<uint16_t*>(xg), done, max_items);
 }
 
 cudaError_t launch_gather(const void* hidden, int64_t stride, int32_t* meta, const int32_t* sorted, int kk,

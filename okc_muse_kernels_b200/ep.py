@@ -6,8 +6,9 @@ output is the sum of the GPUs' partial results); the reference never runs that s
 all-reduce is not run", muse_moe_w4a16/baseline.py:8), so the exchange steps here are new:
 
     1. all-gather of the ranks' token blocks: hidden bf16 [T/world, H] and router logits f32 [T/world, E]
-    2. every rank routes all T tokens identically and runs its local experts on them, plus the
-       replicated shared expert on its own token block only -> FP32 partial sums [T, H]
+       (or, with the router inside the gather kernel, the ids and weights of the rank's own tokens)
+    2. every rank routes all T tokens identically (or sorts the gathered routing) and runs its local experts
+       on them, plus the replicated shared expert on its own token block only -> FP32 partial sums [T, H]
     3. reduce-scatter of the partial sums (FP32, so the cross-GPU sum adds no bf16 rounding)
     4. cast of the rank's own rows to bf16
 
@@ -152,6 +153,30 @@ class PeerExchange:
             C.byref(self.comm), hidden_own.data_ptr(), hidden_own.stride(0), logits_own.data_ptr(),
             torch.cuda.current_stream().cuda_stream), "okc_ep_gather_tokens")
 
+    def route_gather(self, state: dict, hidden_own: torch.Tensor, logits_own: torch.Tensor):
+        """The token all-gather with the router in it (one kernel): routes this rank's own token block, sends
+        rows + ids + weights to every rank, waits for every rank's, sorts the whole step's routes into the
+        state's workspace.  Returns views (ids int32 [T, k], weights f32 [T, k]) of all tokens' routing in this
+        rank's buffer; go on with ``experts_ep`` (or ``moe._experts`` + ``reduce_scatter``)."""
+        plan = state["plan"]
+        if hidden_own.stride(-1) != 1 or not logits_own.is_contiguous():
+            raise ValueError("token rows must be contiguous")
+        _lib.check(_lib.lib().okc_ep_route_gather(
+            C.byref(plan.c_plan()), C.byref(self.comm), hidden_own.data_ptr(), hidden_own.stride(0), logits_own.data_ptr(),
+            state["workspace"].data_ptr(), torch.cuda.current_stream().cuda_stream), "okc_ep_route_gather")
+        return self.routed_views(plan.top_k)
+
+    def routed_views(self, top_k: int):
+        if getattr(self, "_routed", None) is None or self._routed[0] != top_k:
+            a, b = C.c_void_p(), C.c_void_p()
+            _lib.check(_lib.lib().okc_ep_routed_views(C.byref(self.comm), top_k, C.byref(a), C.byref(b)), "okc_ep_routed_views")
+            base, T = self.buf.data_ptr(), self.comm.tokens
+            n = T * top_k * 4
+            ids = self.buf[a.value - base:a.value - base + n].view(torch.int32).view(T, top_k)
+            wts = self.buf[b.value - base:b.value - base + n].view(torch.float32).view(T, top_k)
+            self._routed = (top_k, ids, wts)
+        return self._routed[1], self._routed[2]
+
     def reduce_scatter(self, out: torch.Tensor) -> None:
         _lib.check(_lib.lib().okc_ep_reduce_scatter(C.byref(self.comm), out.data_ptr(),
                                                    torch.cuda.current_stream().cuda_stream), "okc_ep_reduce_scatter")
@@ -262,7 +287,7 @@ class ExpertParallelMoE:
     def __init__(self, plan: MoEPlan, tokens: int, weights: dict | None = None, group=None,
                  local_step: Callable | None = None, cast: Callable | None = None,
                  device: torch.device | str | None = None, exchange: str = "nccl", fuse_combine: bool = True,
-                 guard: "StepGuard | None" = None, wait_limit_ms: int = 0):
+                 guard: "StepGuard | None" = None, wait_limit_ms: int = 0, route_in_gather: bool = True):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -293,6 +318,8 @@ class ExpertParallelMoE:
         # peer exchange: the combine and the reduce-scatter as one kernel (not with the post-expert
         # norm, which needs whole rows before the sum)
         self.fuse_combine = bool(fuse_combine and exchange == "peer" and not plan.post_norm)
+        # peer exchange: the router and the sort inside the token all-gather kernel (needs 2 k <= E)
+        self.route_in_gather = bool(route_in_gather and exchange == "peer" and 2 * plan.top_k <= plan.n_experts)
         self.peer = None
         if exchange == "peer":
             self.peer = PeerExchange(tokens, plan.hidden, plan.n_experts, group=group, device=device,
@@ -316,6 +343,16 @@ class ExpertParallelMoE:
         if self.guard is not None:
             self.guard.check_in()
         if self.peer is not None:
+            if self.route_in_gather:
+                self.peer.route_gather(self.state, hidden_own, logits_own)
+                if self.fuse_combine:
+                    experts_ep(self.hidden_all, self.state, self.peer.comm, self.out)
+                else:
+                    from .moe import _check_hidden, _experts
+                    hidden, stride = _check_hidden(self.hidden_all, self.plan)
+                    _experts(hidden, stride, self.tokens, self.state, self.partial, True)
+                    self.peer.reduce_scatter(self.out)
+                return self.out
             self.peer.gather_tokens(hidden_own, logits_own)
             if self.fuse_combine:
                 route(self.logits_all, self.state, own_tokens=self.own)

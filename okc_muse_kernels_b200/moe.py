@@ -149,13 +149,15 @@ def prepare(weights: dict, plan: MoEPlan | None = None, *, top_k: int = 8, max_t
     return state
 
 
-def _check_hidden(hidden: torch.Tensor, plan: MoEPlan) -> tuple[int, int]:
+def _check_hidden(hidden: torch.Tensor, plan: MoEPlan, allow_f32: bool = False) -> tuple[int, int]:
     _need_cuda(hidden)
-    if hidden.dtype != torch.bfloat16 or hidden.dim() != 2 or hidden.shape[1] != plan.hidden:
-        raise ValueError(f"hidden_states must be bf16 [T, {plan.hidden}]")
+    ok_dtype = hidden.dtype == torch.bfloat16 or (allow_f32 and hidden.dtype == torch.float32)
+    if not ok_dtype or hidden.dim() != 2 or hidden.shape[1] != plan.hidden:
+        raise ValueError(f"hidden_states must be bf16 [T, {plan.hidden}]" + (" (or f32 with a pre-expert norm)" if allow_f32 else ""))
     if hidden.shape[0] < 1 or hidden.shape[0] > plan.max_tokens:
         raise ValueError(f"T = {hidden.shape[0]} outside 1..max_tokens = {plan.max_tokens}")
-    if hidden.stride(1) != 1 or hidden.stride(0) % 8 or hidden.data_ptr() % 16:
+    unit = 8 if hidden.dtype == torch.bfloat16 else 4
+    if hidden.stride(1) != 1 or hidden.stride(0) % unit or hidden.data_ptr() % 16:
         hidden = hidden.contiguous()
     return hidden, hidden.stride(0)
 
@@ -166,8 +168,20 @@ def _own(plan: MoEPlan, T: int, own_tokens) -> tuple[int, int]:
     return (0, T) if own_tokens is None else (int(own_tokens[0]), int(own_tokens[1]))
 
 
-def _experts(hidden, stride, T, state, out, out_f32):
+def _experts(hidden, stride, T, state, out, out_f32, pre_norm=None):
     plan: MoEPlan = state["plan"]
+    if pre_norm is not None:
+        gain, eps = pre_norm
+        _need_cuda(gain)
+        if gain.dtype != torch.float32 or tuple(gain.shape) != (plan.hidden,):
+            raise ValueError(f"pre_norm_gain must be f32 [{plan.hidden}]")
+        gain = gain.contiguous()
+        _lib.check(_lib.lib().okc_moe_experts_prenorm(
+            C.byref(plan.c_plan()), state["packed_w13"].data_ptr(), state["packed_w2"].data_ptr(),
+            state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, int(hidden.dtype == torch.float32),
+            gain.data_ptr(), float(eps), T, _ptr(state["post_norm_w"]), state["workspace"].data_ptr(), out.data_ptr(),
+            int(out_f32), _stream()), "okc_moe_experts_prenorm")
+        return
     _lib.check(_lib.lib().okc_moe_experts(
         C.byref(plan.c_plan()), state["packed_w13"].data_ptr(), state["packed_w2"].data_ptr(),
         state["gs13"].data_ptr(), state["gs2"].data_ptr(), hidden.data_ptr(), stride, T,
@@ -248,11 +262,17 @@ def experts_ep(hidden_all: torch.Tensor, state: dict, comm, out: torch.Tensor) -
     return out
 
 
-def kernel_fn(data: dict, state: dict, *, out_f32: bool = False, own_tokens=None) -> torch.Tensor:
+def kernel_fn(data: dict, state: dict, *, out_f32: bool = False, own_tokens=None, pre_norm_gain: torch.Tensor | None = None,
+              pre_norm_eps: float = 1e-5) -> torch.Tensor:
     """The reference's timed entry (submission.py:6518): routing given as ``topk_ids`` int32 [T, k]
     (global ids; ids outside this shard, -1 included, are skipped) and ``topk_weights`` f32 [T, k].
     Returns a new bf16 [T, H] tensor (f32 partial sums with ``out_f32``); rows with no local route
-    are zero.  Graph-capturable: no host sync, no branching on values."""
+    are zero.  Graph-capturable: no host sync, no branching on values.
+
+    ``pre_norm_gain`` f32 [H]: the layer's pre-expert RMSNorm, applied while the token rows are gathered
+    (rows become bf16(x * rsqrt(mean(x^2) + pre_norm_eps) * gain); muse_decode_layer/layer.py:1700-1745,
+    reference.py:465 with gain = 1 + pre_expert_norm); ``hidden_states`` may then be f32 (the pooler's
+    output), which is rounded to bf16 first.  With ``out_f32`` the result is what the unpooler consumes."""
     plan: MoEPlan = state["plan"]
     cfg = data.get("config")
     if cfg is not None:
@@ -260,7 +280,7 @@ def kernel_fn(data: dict, state: dict, *, out_f32: bool = False, own_tokens=None
                          ("d_hidden", plan.hidden), ("d_expert", plan.inter), ("n_experts", plan.n_experts)):
             if key in cfg and cfg[key] != val:
                 raise ValueError(f"config[{key!r}] = {cfg[key]} but the state was prepared for {val}")
-    hidden, stride = _check_hidden(data["hidden_states"], plan)
+    hidden, stride = _check_hidden(data["hidden_states"], plan, allow_f32=pre_norm_gain is not None)
     T = hidden.shape[0]
     ids = data["topk_ids"]
     wts = data["topk_weights"]
@@ -273,7 +293,7 @@ def kernel_fn(data: dict, state: dict, *, out_f32: bool = False, own_tokens=None
     _lib.check(_lib.lib().okc_moe_sort(C.byref(plan.c_plan()), ids.data_ptr(), wts.data_ptr(), T, t0, t1,
                                        state["workspace"].data_ptr(), _stream()), "okc_moe_sort")
     out = torch.empty((T, plan.hidden), dtype=torch.float32 if out_f32 else torch.bfloat16, device=hidden.device)
-    _experts(hidden, stride, T, state, out, out_f32)
+    _experts(hidden, stride, T, state, out, out_f32, None if pre_norm_gain is None else (pre_norm_gain, pre_norm_eps))
     return out
 
 
@@ -341,22 +361,23 @@ def moe_layer_step(hidden_states: torch.Tensor, router_w: torch.Tensor, state: d
 
 
 def moe_step(hidden_states: torch.Tensor, router_logits: torch.Tensor, state: dict, *, out_f32: bool = False,
-             own_tokens=None, out: torch.Tensor | None = None) -> torch.Tensor:
+             own_tokens=None, out: torch.Tensor | None = None, pre_norm_gain: torch.Tensor | None = None,
+             pre_norm_eps: float = 1e-5) -> torch.Tensor:
     """One MoE decode step: bf16 hidden [T, H] + f32 router logits [T, E] -> bf16 [T, H].
 
     Router: softmax over the experts, top-k (ties to the lowest index), weights renormalised over
     the selected; experts: SiLU(gate)*up, FP32 accumulation; rows are the routing-weighted sum of
     this shard's experts (+ the shared expert for ``own_tokens``).  ``out_f32`` returns the FP32
-    partial sum an expert-parallel reduce-scatter consumes."""
+    partial sum an expert-parallel reduce-scatter consumes.  ``pre_norm_gain``: see ``kernel_fn``."""
     plan: MoEPlan = state["plan"]
-    hidden, stride = _check_hidden(hidden_states, plan)
+    hidden, stride = _check_hidden(hidden_states, plan, allow_f32=pre_norm_gain is not None)
     T = hidden.shape[0]
     if router_logits.shape[0] != T:
         raise ValueError("hidden_states and router_logits disagree on T")
     route(router_logits, state, own_tokens=own_tokens)
     if out is None:
         out = torch.empty((T, plan.hidden), dtype=torch.float32 if out_f32 else torch.bfloat16, device=hidden.device)
-    _experts(hidden, stride, T, state, out, out_f32)
+    _experts(hidden, stride, T, state, out, out_f32, None if pre_norm_gain is None else (pre_norm_gain, pre_norm_eps))
     return out
 
 

@@ -190,6 +190,18 @@ def post_expert_norm(y: np.ndarray, w_bf16: np.ndarray) -> np.ndarray:
     return (y * (np.float32(1.0) / np.sqrt(ms + POST_NORM_EPS))).astype(np.float32)
 
 
+def pre_expert_norm(hidden, gain: np.ndarray, eps: float = 1e-5) -> np.ndarray:
+    """The layer's pre-expert RMSNorm as the experts see it: bf16 bits of x * rsqrt(mean(x^2) + eps) * gain,
+    x being the token rows (bf16 bits, or float32 rounded to bf16 first).  Follows ``p = _rms(p) * (1 +
+    pre_expert_norm)`` (muse_decode_layer/reference.py:189-191,465) with the rounding points of the
+    reference's fused gather (muse_decode_layer/layer.py:1700-1745)."""
+    h = np.asarray(hidden)
+    x = bf16_to_f32(h) if h.dtype == np.uint16 else bf16_to_f32(f32_to_bf16(h.astype(np.float32)))
+    ms = np.mean(x.astype(np.float64) ** 2, axis=-1, keepdims=True)
+    r = (1.0 / np.sqrt(ms + eps)).astype(np.float32)
+    return f32_to_bf16((x * r * np.asarray(gain, np.float32)).astype(np.float32))
+
+
 def expert_mlp(x: np.ndarray, w13, w13_sf, w13_gs, w2, w2_sf, w2_gs) -> np.ndarray:
     """One expert on rows x (float32 [n,H]) -> float32 [n,H]: h = x W13^T, silu(gate)*up, @ W2^T
     (muse_moe_w4a16/reference.py:103-105)."""

@@ -57,7 +57,9 @@ def main():
     mine = synth.make_weights(wl, seed=21, device=dev, n_experts=plan.local_count, first_expert=plan.local_start)
     peer = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer")                # fused combine + reduce
     split = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer", fuse_combine=False)
+    plain = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="peer", route_in_gather=False)     # router as its own kernels
     nccl = ep.ExpertParallelMoE(plan, T, weights=mine, exchange="nccl")
+    assert peer.route_in_gather and not plain.route_in_gather
     t0, t1 = peer.own
     wn = synth.to_numpy_weights(w)
     shared = {k[len("shared_"):]: v for k, v in wn.items() if k.startswith("shared_")}
@@ -68,11 +70,14 @@ def main():
         a = peer.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
         b = nccl.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
         c = split.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
-        rc, detail = peer.peer.read_status()
-        ok &= rc == 0
-        rc, detail = split.peer.read_status()
-        ok &= rc == 0
+        d = plain.step(hidden[t0:t1].contiguous(), logits[t0:t1].contiguous()).clone()
+        for layer in (peer, split, plain):
+            rc, detail = layer.peer.read_status()
+            ok &= rc == 0
         ok &= bool(torch.equal(a, c))                           # same sums in the same order
+        ok &= bool(torch.equal(a, d))                           # the router inside the gather kernel routes the same
+        ids_ref, _ = moe_np.route_softmax_topk(logits.cpu().numpy(), K)
+        ok &= bool(np.array_equal(peer.peer.routed_views(K)[0].cpu().numpy(), ids_ref))
         if world == 2:
             ok &= bool(torch.equal(a, b))                       # two addends: the order cannot matter
         ok &= bool(torch.allclose(a.float(), b.float(), rtol=2 ** -7, atol=1e-5))

@@ -84,6 +84,55 @@ def test_single_rank_exchange_equals_the_plain_step():
         assert torch.equal(out, want), f"step {step}: unfused"
 
 
+def test_routed_gather_single_rank_and_two_emulated_ranks():
+    """The gather kernel with the router in it (top-k of the own tokens, ids + weights sent instead of
+    logits, sort of the whole step by the CTA that saw every flag).  world = 1: equal to the plain step bit
+    for bit.  Two emulated ranks: a first pass moves everybody's rows and routing into both buffers (the
+    rank that runs first sorts before the other's routing has arrived, its tables are thrown away), a
+    second pass over the same inputs then sorts complete data on both ranks."""
+    dev = _dev()
+    wl = synth.Workload("ep5", 24, 512, 256, 16, 4, shared_inter=256)
+    (ex, state, own), = _ranks(1, wl, wl.tokens, dev)
+    _, full = _full_layer(wl, wl.tokens, dev)
+    out = torch.empty((wl.tokens, wl.hidden), dtype=torch.bfloat16, device=dev)
+    for step in range(3):
+        hidden, logits = synth.make_inputs(wl, seed=600 + step, device=dev)
+        want = okc.moe_step(hidden, logits, full)
+        ids, wts = ex.route_gather(state, hidden, logits)
+        okc.experts_ep(ex.hidden_all, state, ex.comm, out)
+        _status_ok(ex, state)
+        assert torch.equal(ids, full["ids"][:wl.tokens]) and torch.equal(wts, full["wts"][:wl.tokens])
+        assert torch.equal(out, want), f"step {step}"
+        ref = moe_np.sort_routes(ids.cpu().numpy(), 0, wl.n_experts)
+        s = okc.sorted_routes(state, wl.tokens)
+        assert np.array_equal(s["counts"].cpu().numpy()[:wl.n_experts], ref["counts"])
+    # two emulated ranks
+    wl = synth.Workload("ep6", 16, 512, 256, 16, 4, shared_inter=256)
+    (ex0, st0, own0), (ex1, st1, own1) = _ranks(2, wl, wl.tokens, dev)
+    w_full, full = _full_layer(wl, wl.tokens, dev)
+    tb = wl.tokens // 2
+    out0 = torch.empty((tb, wl.hidden), dtype=torch.bfloat16, device=dev)
+    out1 = torch.empty_like(out0)
+    for step in range(2):
+        hidden, logits = synth.make_inputs(wl, seed=700 + step, device=dev)
+        h0, l0 = hidden[own0[0]:own0[1]], logits[own0[0]:own0[1]].contiguous()
+        h1, l1 = hidden[own1[0]:own1[1]], logits[own1[0]:own1[1]].contiguous()
+        for _ in range(2):
+            ex0.mark_arrived("tokens", 1)
+            ex0.route_gather(st0, h0, l0)
+            ids1, _ = ex1.route_gather(st1, h1, l1)
+        ids_ref, _ = moe_np.route_softmax_topk(logits.cpu().numpy(), wl.top_k)
+        assert np.array_equal(ids1.cpu().numpy(), ids_ref) and np.array_equal(ex0.routed_views(wl.top_k)[0].cpu().numpy(), ids_ref)
+        okc.moe._experts(ex1.hidden_all, ex1.hidden_all.stride(0), wl.tokens, st1, ex1.partial, True)
+        ex0.mark_arrived("partial", 1)
+        okc.experts_ep(ex0.hidden_all, st0, ex0.comm, out0)
+        ex1.reduce_scatter(out1)
+        _status_ok(ex0, st0)
+        _status_ok(ex1, st1)
+        want = okc.moe_step(hidden, logits, full)
+        assert torch.allclose(torch.cat([out0, out1]).float(), want.float(), rtol=2 ** -7, atol=1e-5), f"step {step}"
+
+
 @pytest.mark.parametrize("fused_first_rank", [False, True])
 def test_two_emulated_ranks_one_after_the_other(fused_first_rank):
     dev = _dev()

@@ -732,3 +732,37 @@ def test_graph_replay_with_fresh_inputs_is_bitwise_eager():
         torch.cuda.synchronize()
         assert torch.equal(out_buf, eager[i]), f"replay {r} (input {i})"
     _status_ok(state)
+
+
+@pytest.mark.parametrize("rows_f32", [False, True])
+def test_pre_expert_norm_in_the_gather_and_f32_rows_out(rows_f32):
+    """The steps either side of the MoE block in the reference's layer: the pre-expert RMSNorm applied while
+    the token rows are gathered (bf16 rows, or the pooler's FP32 rows rounded to bf16 first;
+    muse_decode_layer/layer.py:1700-1745, reference.py:465) and FP32 output rows for the unpooler."""
+    dev = _dev()
+    wl = synth.Workload("pre", 40, 1024, 512, 16, 4)
+    w = synth.make_weights(wl, seed=71, device=dev)
+    state = okc.prepare(w, okc.MoEPlan(hidden=wl.hidden, inter=wl.inter, n_experts=16, top_k=4, max_tokens=64))
+    g = torch.Generator(device="cpu").manual_seed(72)
+    x32 = (torch.randn((wl.tokens, wl.hidden), generator=g) * 3.0 + 0.5)
+    gain = (1.0 + 0.1 * torch.randn((wl.hidden,), generator=g)).float()
+    _, logits = synth.make_inputs(wl, seed=73, device=dev)
+    hidden = x32.to(dev) if rows_f32 else x32.to(torch.bfloat16).to(dev)
+    out = okc.moe_step(hidden, logits, state, out_f32=True, pre_norm_gain=gain.to(dev), pre_norm_eps=1e-5)
+    _status_ok(state)
+    assert out.dtype == torch.float32 and out.shape == (wl.tokens, wl.hidden)
+    rows = x32.numpy() if rows_f32 else _bits(hidden)
+    normed = moe_np.pre_expert_norm(rows, gain.numpy(), 1e-5)
+    # the oracle's rows agree with torch's statement of the layer: _rms(p) * (1 + w), rounded to bf16
+    xb = x32.to(torch.bfloat16).float()
+    want = (xb * torch.rsqrt(xb.pow(2).mean(-1, keepdim=True) + 1e-5) * gain).to(torch.bfloat16)
+    assert (np.abs(moe_np.bf16_to_f32(normed) - want.float().numpy()) <= np.abs(want.float().numpy()) * 2.0 ** -7).all()
+    _, ref, ids, _ = moe_np.moe_step(normed, logits.cpu().numpy(), synth.to_numpy_weights(w), wl.top_k)
+    assert np.array_equal(state["ids"][:wl.tokens].cpu().numpy(), ids)
+    got = out.cpu().numpy().astype(np.float64)
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= REL_L2 and np.abs(got - ref).max() <= MAX_ABS, f"rel-L2 {rel:.3e}"
+    # without the norm the same call gives something else, with it twice the same bits
+    assert torch.equal(out, okc.moe_step(hidden, logits, state, out_f32=True, pre_norm_gain=gain.to(dev)))
+    if not rows_f32:
+        assert not torch.equal(out, okc.moe_step(hidden, logits, state, out_f32=True))
