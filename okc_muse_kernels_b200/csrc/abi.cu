@@ -151,7 +151,7 @@ const char* okc_moe_strerror(int code) {
   }
 }
 
-int okc_moe_launches_per_step(void) { return 5; }
+int okc_moe_launches_per_step(void) { return 5; }   // top-k, sort, gather, GEMMs, combine (top-k + sort are one kernel up to 32 tokens)
 
 int okc_moe_query(const okc_moe_plan* plan, okc_moe_sizes* out) {
   Geometry g;

@@ -124,6 +124,23 @@ __global__ void __launch_bounds__(256) okc_route_topk(const float* __restrict__ 
                   ids_out + t * k, wts_out + t * k);
 }
 
+// Router and sort of a small step in one CTA (T <= 32: a warp per token does the top-k, then all warps
+// sort): one launch and its gap fewer than okc_route_topk + okc_route_sort, which is what a step of a few
+// tokens is made of.  Beyond 32 tokens the top-k of all tokens on one SM costs more than the launch.
+template <int PER>
+__global__ void __launch_bounds__(kRouteThreads, 1) okc_route_topk_sort(const RouteParams p, const float* __restrict__ logits,
+                                                                       int n_part) {
+  extern __shared__ int32_t sm[];
+  griddep_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < p.T)
+    topk_token<PER>(logits + static_cast<size_t>(warp) * p.E, n_part, static_cast<size_t>(p.T) * p.E, p.E, p.k, p.router_mode,
+                    p.router_mult, p.router_bias, lane, p.ids_out + warp * p.k, p.wts_out + warp * p.k);
+  __threadfence();
+  __syncthreads();
+  sort_routes_cta<kRouteThreads>(p, sm);
+}
+
 __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_sort(const RouteParams p) {
   extern __shared__ int32_t sm[];
   griddep_wait();   // the ids may come from the top-k kernel launched just before
@@ -274,6 +291,22 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
       e = cudaGetLastError();
       if (e != cudaSuccess) return e;
       lg = p.router_part;
+    }
+    if (p.T <= kRouteThreads / 32) {
+      // a small step: top-k and sort in one CTA
+      RouteParams q = p;
+      q.logits = nullptr; q.router_w = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
+      const dim3 one(1), threads(kRouteThreads);
+      if (p.E <= 128) {
+        e = cudaFuncSetAttribute(okc_route_topk_sort<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<4>, one, threads, smem, stream, n_part > 0, q, lg, n_part);
+      }
+      if (p.E <= 256) {
+        e = cudaFuncSetAttribute(okc_route_topk_sort<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<8>, one, threads, smem, stream, n_part > 0, q, lg, n_part);
+      }
+      e = cudaFuncSetAttribute(okc_route_topk_sort<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<16>, one, threads, smem, stream, n_part > 0, q, lg, n_part);
     }
     const dim3 grid((p.T + 7) / 8), block(256);
     if (p.E <= 128)
