@@ -639,15 +639,18 @@ def run_gpu(args):
             failed = failed or not a["parity"]["ok"]
         extra["sweep"] = rows
 
-    # kernels of this library per step against the single-GPU step's five (top-k, sort, gather, GEMMs, combine).
-    # Peer exchange: + the token push, + the pull-reduce unless the combine is fused with the reduce-scatter,
-    # - top-k and sort when the router runs inside the push kernel.  NCCL exchange: + the cast.
+    # kernels of this library per step.  One GPU: top-k + sort (one kernel up to 32 tokens, else two), gather, the
+    # GEMM launch, combine, + the router's logits kernel with --route-from-hidden.  Expert parallel, peer
+    # exchange: push + router + sort (one kernel), gather, GEMMs, combine + reduce-scatter; the NCCL exchange:
+    # the single-GPU kernels + the cast.
     layer = m["layer"]
-    ep_extra_launches = 0
-    if world > 1:
-        ep_extra_launches = 1
-        if layer.exchange == "peer":
-            ep_extra_launches = (1 if layer.fuse_combine else 2) - (2 if layer.route_in_gather else 0)
+    single = (1 if tokens <= 32 else 2) + 3 + (1 if args.route_from_hidden else 0)
+    if world == 1:
+        launches_per_step = single
+    elif layer.exchange == "peer":
+        launches_per_step = (1 if layer.route_in_gather else 1 + (1 if tokens <= 32 else 2)) + 2 + (1 if layer.fuse_combine else 1)
+    else:
+        launches_per_step = single + 1
     if rank == 0:
         line = {"metric": METRIC, "value": m["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": m["ms_per_step"], "higher_is_better": True,
@@ -657,7 +660,7 @@ def run_gpu(args):
                            "us_per_step": 1e3 * m["ms_per_step"], "step_ms_median": statistics.median(m["times_ms"]),
                            "step_ms_min": min(m["times_ms"])},
                 "roofline": m["roofline"], "cpu_baseline": cpu, "e2e": m["e2e"], "parity": m["parity"], "clocks": m["clocks"],
-                "gpu_launches": (_lib.lib().okc_moe_launches_per_step() + ep_extra_launches) * args.steps}
+                "gpu_launches": launches_per_step * args.steps}
         if m["per_rank"] is not None:
             line["per_rank"] = m["per_rank"]
         line.update(extra)

@@ -297,7 +297,8 @@ int okc_moe_read_status(const void* workspace, okc_stream_t stream, int32_t* det
  * the status.  The reference's waits are unbounded spins (submission.py:3862-3869, 394-398). */
 int okc_moe_probe_wait_timeout(void* workspace, okc_stream_t stream);
 
-/* Kernels launched by the last okc_moe_experts / okc_moe_step shape: a constant of the build. */
+/* Kernels launched by okc_moe_step for a step of more than 32 tokens (top-k, sort, gather, the GEMM launch,
+ * combine); up to 32 tokens top-k and sort are one kernel. */
 int okc_moe_launches_per_step(void);
 
 #ifdef __cplusplus

@@ -47,13 +47,20 @@ def _compile(src: str) -> tuple[str, str]:
     return obj, r.stderr
 
 
-def build(force: bool = False, verbose: bool = False, wait_profile: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, wait_profile: bool = False, variant: str | None = None,
+          defines: tuple[str, ...] = ()) -> str:
     """Compiles and links the library; returns its path.  ``wait_profile`` builds the instrumented
     variant libokc_moe_b200_prof.so (-DOKC_WAIT_PROFILE: per-role wait cycles, read back with
-    okc_moe_debug_wait_profile); load it by pointing OKC_MOE_LIB at it."""
+    okc_moe_debug_wait_profile); load it by pointing OKC_MOE_LIB at it.  ``variant`` + ``defines`` build
+    libokc_moe_b200_<variant>.so with extra -D switches (tuning experiments: the kernels' compile-time
+    knobs), to be compared against the default build through OKC_MOE_LIB."""
     global OBJ
     lib_path = LIB
-    if wait_profile:
+    if variant:
+        lib_path = LIB.replace(".so", f"_{variant}.so")
+        OBJ = os.path.join(PKG, "build", variant)
+        NVCC_FLAGS.extend(f"-D{d}" for d in defines)
+    elif wait_profile:
         lib_path = LIB.replace(".so", "_prof.so")
         OBJ = os.path.join(PKG, "build", "prof")
         NVCC_FLAGS.append("-DOKC_WAIT_PROFILE")
@@ -75,4 +82,7 @@ def build(force: bool = False, verbose: bool = False, wait_profile: bool = False
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, wait_profile="--wait-profile" in sys.argv))
+    # python -m okc_muse_kernels_b200.build [--force] [-v] [--wait-profile] [--variant NAME -DKNOB=VALUE ...]
+    name = sys.argv[sys.argv.index("--variant") + 1] if "--variant" in sys.argv else None
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, wait_profile="--wait-profile" in sys.argv,
+                variant=name, defines=tuple(a[2:] for a in sys.argv if a.startswith("-D"))))
