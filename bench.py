@@ -370,6 +370,8 @@ def measure(wl, tokens, args, dev, world, rank, *, state=None, layer=None, with_
             raise SystemExit("--route-from-hidden is a single-GPU option")
         gr = torch.Generator(device=dev).manual_seed(4242)
         router_w = torch.randn((wl.n_experts, wl.hidden), generator=gr, device=dev) * (wl.hidden ** -0.5)
+        if args.route_from_hidden == "mma":      # bf16 hi + lo rows: the logits on the tensor cores
+            router_w = okc.split_router(router_w)
 
     def one_step(h, lg, o):
         if router_w is not None:
@@ -696,8 +698,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-c4-anchor", action="store_true", help="N = 1: skip the configuration-4 single-GPU step (`c4_n1`)")
     ap.add_argument("--sweep", action="store_true", help="N = 1: add configuration 3 (T = 1 ... 256) as `sweep`")
-    ap.add_argument("--route-from-hidden", action="store_true",
-                    help="N = 1: compute the router logits from the token rows inside the step (okc.moe_layer_step)")
+    ap.add_argument("--route-from-hidden", nargs="?", const="fma", default=None, choices=["fma", "mma"],
+                    help="N = 1: compute the router logits from the token rows inside the step (okc.moe_layer_step): "
+                         "FP32 multiply-adds on CUDA cores (fma) or bf16 hi + lo on the tensor cores (mma)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the all-gather / reduce-scatter through this library's peer-memory kernels or NCCL")
     ap.add_argument("--ep-graphs", type=int, default=1, choices=[0, 1],

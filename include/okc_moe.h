@@ -106,8 +106,9 @@ int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weig
  *   mode 0: softmax top-k as okc_moe_route.
  *   mode 1: scores = sigmoid(multiplier * logit); the top_k of scores + bias are chosen (ties to the
  *           lowest id); weights = chosen scores / (their sum + 1e-15).
- * w: f32 [E, H] (NULL: take `logits` f32 [T, E] instead and only apply the mode); bias: f32 [E] or NULL.
- * With w: T <= 256, E a multiple of 16; the per-route output area of `workspace` is used as scratch.
+ * w: f32 [E, H], or w_split (see okc_router), or neither: take `logits` f32 [T, E] instead and only apply the
+ * mode; bias: f32 [E] or NULL.
+ * With w / w_split: T <= 256, E a multiple of 16; the per-route output area of `workspace` is used as scratch.
  * Then sorts the routes as okc_moe_route does.
  */
 typedef struct okc_router {
@@ -115,7 +116,12 @@ typedef struct okc_router {
   const float* bias;
   int32_t mode;
   float multiplier;
+  const void* w_split;   /* instead of w: the router matrix as bf16 hi + lo rows [2 E, H] (okc_moe_router_split);
+                            the logits are then computed on the tensor cores, two bf16 MMAs per K step */
 } okc_router;
+/* w f32 [E, H] -> w_split bf16 [2 E, H]: rows [0, E) = bf16(w), rows [E, 2 E) = bf16(w - bf16(w)); once per router
+ * matrix.  Replaces the split in `_router_split` (muse_decode_layer/layer.py:325-351). */
+int okc_moe_router_split(const float* w, int n_experts, int hidden, void* w_split, okc_stream_t stream);
 int okc_moe_route_hidden(const okc_moe_plan* plan, const okc_router* router, const void* hidden,
                          int64_t hidden_stride, const float* logits, int T, int own_t0, int own_t1,
                          int32_t* ids, float* weights, void* workspace, okc_stream_t stream);

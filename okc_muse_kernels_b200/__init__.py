@@ -7,7 +7,7 @@
 The CUDA kernels live in csrc/ and are reached through the C ABI of include/okc_moe.h
 (libokc_moe_b200.so, built by ``python -m okc_muse_kernels_b200.build``).
 """
-from .moe import HostStep, MoEPlan, OkcError, cast_bf16, experts_ep, experts_profiled, kernel_fn, moe_layer_step, moe_step, prepare, read_status, route, route_hidden, sorted_routes, unpack_bf16
+from .moe import HostStep, MoEPlan, OkcError, cast_bf16, experts_ep, experts_profiled, kernel_fn, moe_layer_step, moe_step, prepare, read_status, route, route_hidden, sorted_routes, split_router, unpack_bf16
 
 __all__ = ["HostStep", "MoEPlan", "OkcError", "cast_bf16", "experts_ep", "experts_profiled", "kernel_fn", "moe_layer_step", "moe_step", "prepare", "read_status", "route", "route_hidden", "sorted_routes",
-           "unpack_bf16"]
+           "split_router", "unpack_bf16"]

@@ -46,7 +46,8 @@ class EpComm(C.Structure):
 
 class Router(C.Structure):
     """okc_router"""
-    _fields_ = [("w", C.c_void_p), ("bias", C.c_void_p), ("mode", C.c_int32), ("multiplier", C.c_float)]
+    _fields_ = [("w", C.c_void_p), ("bias", C.c_void_p), ("mode", C.c_int32), ("multiplier", C.c_float),
+                ("w_split", C.c_void_p)]
 
 
 _P = C.c_void_p
@@ -61,6 +62,7 @@ SIGNATURES = {
     "okc_moe_repack": (C.c_int, [_PLAN, _P, _P, _P, _P, C.c_int, C.c_int, _P, _P, _P]),
     "okc_moe_route": (C.c_int, [_PLAN, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
     "okc_moe_route_hidden": (C.c_int, [_PLAN, C.POINTER(Router), _P, C.c_int64, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P]),
+    "okc_moe_router_split": (C.c_int, [_P, C.c_int, C.c_int, _P, _P]),
     "okc_moe_sort": (C.c_int, [_PLAN, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "okc_moe_experts": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P]),
     "okc_moe_experts_prenorm": (C.c_int, [_PLAN, _P, _P, _P, _P, _P, C.c_int64, C.c_int, _P, C.c_float, C.c_int, _P, _P, _P,

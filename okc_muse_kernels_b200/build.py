@@ -18,7 +18,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libokc_moe_b200.so")
-SOURCES = ("abi.cu", "route.cu", "repack.cu", "gemm.cu", "ep.cu")
+SOURCES = ("abi.cu", "route.cu", "repack.cu", "gemm.cu", "ep.cu", "router_mma.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

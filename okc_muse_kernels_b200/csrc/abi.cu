@@ -28,12 +28,14 @@ static EncodeFn encode_fn() {
   return f;
 }
 
-// bf16 [rows, K] row-major, box = 64 elements x box_rows, 128-byte swizzle, zero fill outside.
-static bool encode_rows_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+// bf16 [rows, K] row-major (rows row_stride elements apart; 0: K), box = 64 elements x box_rows, 128-byte swizzle,
+// zero fill outside.
+static bool encode_rows_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t K, uint32_t box_rows,
+                            uint64_t row_stride = 0) {
   EncodeFn f = encode_fn();
   if (!f) return false;
   const cuuint64_t dims[2] = {K, rows};
-  const cuuint64_t strides[1] = {K * 2};
+  const cuuint64_t strides[1] = {(row_stride ? row_stride : K) * 2};
   const cuuint32_t box[2] = {64, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   return f(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -112,7 +114,28 @@ static int route_common(const okc_moe_plan* plan, const float* logits, const int
   if (router) {
     if (router->mode != 0 && router->mode != 1) return OKC_ERR_BAD_ARG;
     p.router_mode = router->mode; p.router_mult = router->multiplier; p.router_bias = router->bias;
-    if (router->w) {
+    if (router->w_split) {
+      // logits from the token rows on the tensor cores; split-K partial sums in the (not yet used) per-route output area
+      if (!hidden || !aligned(hidden, 16) || !aligned(router->w_split, 16) || hidden_stride < g.H || (hidden_stride % 8) != 0)
+        return OKC_ERR_BAD_ARG;
+      if (T > 256 || (p.E % 16) != 0) return OKC_ERR_BAD_PLAN;
+      const int n_kb = g.H / 64, tiles = (p.E + 127) / 128;
+      int per = (n_kb + 31) / 32;
+      if (per < (tiles * n_kb + 147) / 148) per = (tiles * n_kb + 147) / 148;
+      if (per > 3) per = 3;
+      if (per < 1) per = 1;
+      const long long splits = (n_kb + per - 1) / per;
+      const long long room = static_cast<long long>(g.kk) * g.H / p.E;   // [T * kk, H] floats hold `room` arrays [T, E]
+      if (splits > room) return OKC_ERR_BAD_PLAN;
+      const uint32_t tpad = static_cast<uint32_t>((T + 15) & ~15);
+      if (!encode_rows_map(&p.router_wmap, const_cast<void*>(router->w_split), 2ull * p.E, static_cast<uint64_t>(g.H), 128) ||
+          !encode_rows_map(&p.router_hmap, const_cast<void*>(hidden), static_cast<uint64_t>(T), static_cast<uint64_t>(g.H), tpad,
+                           static_cast<uint64_t>(hidden_stride)))
+        return OKC_ERR_CUDA;
+      p.router_w_split = static_cast<const uint16_t*>(router->w_split); p.router_kb_per_cta = per;
+      p.hidden = static_cast<const uint16_t*>(hidden); p.hidden_stride = hidden_stride;
+      p.router_splits = static_cast<int>(splits); p.router_part = carve(workspace, g).y;
+    } else if (router->w) {
       // logits from the token rows: split-K partial sums kept in the (not yet used) per-route output area
       if (!hidden || !aligned(hidden, 16) || !aligned(router->w, 16) || hidden_stride < g.H || (hidden_stride % 8) != 0)
         return OKC_ERR_BAD_ARG;
@@ -209,6 +232,12 @@ int okc_moe_route(const okc_moe_plan* plan, const float* logits, int T, int own_
                       reinterpret_cast<cudaStream_t>(stream));
 }
 
+int okc_moe_router_split(const float* w, int n_experts, int hidden, void* w_split, okc_stream_t stream) {
+  if (!w || !w_split || n_experts <= 0 || hidden <= 0 || !aligned(w_split, 16)) return OKC_ERR_BAD_ARG;
+  return launch_router_split(w, w_split, static_cast<size_t>(n_experts) * hidden, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? OKC_OK : OKC_ERR_CUDA;
+}
+
 int okc_moe_sort(const okc_moe_plan* plan, const int32_t* ids, const float* weights, int T, int own_t0, int own_t1,
                  void* workspace, okc_stream_t stream) {
   if (!ids || !weights) return OKC_ERR_BAD_ARG;
@@ -220,7 +249,7 @@ int okc_moe_route_hidden(const okc_moe_plan* plan, const okc_router* router, con
                          const float* logits, int T, int own_t0, int own_t1, int32_t* ids, float* weights,
                          void* workspace, okc_stream_t stream) {
   if (!router || !ids || !weights) return OKC_ERR_BAD_ARG;
-  if ((router->w == nullptr) == (logits == nullptr)) return OKC_ERR_BAD_ARG;   // exactly one source of logits
+  if (((router->w != nullptr) + (router->w_split != nullptr) + (logits != nullptr)) != 1) return OKC_ERR_BAD_ARG;   // one source of logits
   if (!is_sm100()) return OKC_ERR_NO_DEVICE;
   return route_common(plan, logits, nullptr, nullptr, T, own_t0, own_t1, ids, weights, workspace,
                       reinterpret_cast<cudaStream_t>(stream), router, hidden, hidden_stride);

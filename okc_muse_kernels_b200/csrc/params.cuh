@@ -29,7 +29,14 @@ struct RouteParams {
   int64_t hidden_stride;
   int H, router_splits;
   float* router_part;             // scratch f32 [router_splits, T, E]
+  // the same logits on the tensor cores: router_w as bf16 hi + lo rows [2 E, H]
+  const uint16_t* router_w_split;
+  CUtensorMap router_wmap, router_hmap;
+  int router_kb_per_cta;
 };
+cudaError_t launch_router_mma(const CUtensorMap& wmap, const CUtensorMap& hmap, float* part, int32_t* meta, int T, int E, int H,
+                              int kb_per_cta, cudaStream_t stream);
+cudaError_t launch_router_split(const float* w, void* out, size_t n, cudaStream_t stream);
 cudaError_t launch_route(const RouteParams& p, cudaStream_t stream);
 cudaError_t launch_gather(const void* hidden, int64_t stride, int32_t* meta, const int32_t* sorted, int kk,
                           int H, int R, void* xg, int32_t* done, int max_items, cudaStream_t stream);

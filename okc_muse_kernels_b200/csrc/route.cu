@@ -275,11 +275,17 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
   const size_t smem = route_smem_bytes(p.T * p.kk, p.slots, kRouteThreads);
   cudaError_t e = cudaFuncSetAttribute(okc_route_sort, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  if (p.logits != nullptr || p.router_w != nullptr) {
+  if (p.logits != nullptr || p.router_w != nullptr || p.router_w_split != nullptr) {
     // the router proper: ids / weights of every token, then the sort below reads them back
     const float* lg = p.logits;
     int n_part = 0;
-    if (p.router_w != nullptr) {
+    if (p.router_w_split != nullptr) {
+      // logits = hidden . router_w^T on the tensor cores (bf16 hi + lo), split-K partial sums in scratch
+      n_part = p.router_splits;
+      e = launch_router_mma(p.router_wmap, p.router_hmap, p.router_part, p.meta, p.T, p.E, p.H, p.router_kb_per_cta, stream);
+      if (e != cudaSuccess) return e;
+      lg = p.router_part;
+    } else if (p.router_w != nullptr) {
       // logits = hidden . router_w^T as split-K partial sums in scratch; the top-k kernel adds the splits
       n_part = p.router_splits;
       const int kc = ((p.H / kRtK + n_part - 1) / n_part) * kRtK;
@@ -295,7 +301,7 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
     if (p.T <= kRouteThreads / 32) {
       // a small step: top-k and sort in one CTA
       RouteParams q = p;
-      q.logits = nullptr; q.router_w = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
+      q.logits = nullptr; q.router_w = nullptr; q.router_w_split = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
       const dim3 one(1), threads(kRouteThreads);
       if (p.E <= 128) {
         e = cudaFuncSetAttribute(okc_route_topk_sort<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -320,7 +326,7 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
                         p.router_mult, p.router_bias, p.ids_out, p.wts_out);
     if (e != cudaSuccess) return e;
     RouteParams q = p;
-    q.logits = nullptr; q.router_w = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
+    q.logits = nullptr; q.router_w = nullptr; q.router_w_split = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
     return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, q);
   }
   return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, p);

@@ -268,8 +268,11 @@ __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* s
       s_wide = wide_step ? 1 : 0;
       p.meta[kMetaItems] = incl < p.max_items ? incl : p.max_items;
       p.meta[kMetaLocalRoutes] = offs[p.slots];
-      p.meta[kMetaStatus] = 0;
-      p.meta[kMetaDetail] = 0;
+      // a new step: clean status words, unless the router-logits kernel of this very step gave up
+      const int router_gave_up = p.meta[kMetaRouterStatus];
+      p.meta[kMetaStatus] = router_gave_up ? OKC_ERR_TIMEOUT : 0;
+      p.meta[kMetaDetail] = router_gave_up;
+      p.meta[kMetaRouterStatus] = 0;
       p.meta[kMetaTokens] = p.T;
       // the widest item is the first one of the heaviest expert
       p.meta[kMetaWcap] = item_pad(min(cmax, item_rows(cmax, wide_step, p.chunk_rows)));

@@ -19,7 +19,7 @@ import torch
 from . import _lib
 from ._lib import OkcError, Plan, Sizes
 
-__all__ = ["MoEPlan", "prepare", "kernel_fn", "moe_step", "route", "sorted_routes", "unpack_bf16", "read_status",
+__all__ = ["MoEPlan", "prepare", "kernel_fn", "moe_step", "route", "sorted_routes", "unpack_bf16", "read_status", "split_router",
            "experts_profiled", "experts_ep", "cast_bf16", "HostStep", "route_hidden", "moe_layer_step", "OkcError"]
 
 
@@ -318,9 +318,24 @@ def route(router_logits: torch.Tensor, state: dict, *, own_tokens=None):
 SIGMOID_MULTIPLIER = 0.1767766952966369   # the reference layer's ROUTER_MULTIPLIER (muse_decode_layer/reference.py:51)
 
 
+def split_router(router_w: torch.Tensor) -> torch.Tensor:
+    """f32 [E, H] router matrix -> bf16 [2 E, H] (rows [0, E) = bf16(w), rows [E, 2 E) = bf16(w - bf16(w))): once per
+    router matrix; ``route_hidden`` / ``moe_layer_step`` given this tensor compute the logits on the tensor cores,
+    two bf16 MMAs per K step (the reference's `_router_split`, muse_decode_layer/layer.py:325-351)."""
+    _need_cuda(router_w)
+    if router_w.dtype != torch.float32 or router_w.dim() != 2:
+        raise ValueError("router_w must be f32 [E, H]")
+    router_w = router_w.contiguous()
+    out = torch.empty((2 * router_w.shape[0], router_w.shape[1]), dtype=torch.bfloat16, device=router_w.device)
+    _lib.check(_lib.lib().okc_moe_router_split(router_w.data_ptr(), router_w.shape[0], router_w.shape[1], out.data_ptr(), _stream()),
+               "okc_moe_router_split")
+    return out
+
+
 def route_hidden(hidden_states: torch.Tensor, router_w: torch.Tensor, state: dict, *, bias: torch.Tensor | None = None,
                  mode: str = "softmax", multiplier: float = SIGMOID_MULTIPLIER, own_tokens=None):
-    """Router logits ``hidden . router_w^T`` (FP32, never materialised) + top-k + the token->expert sort.
+    """Router logits ``hidden . router_w^T`` (never materialised) + top-k + the token->expert sort.  ``router_w``:
+    f32 [E, H] (FP32 multiply-adds on CUDA cores) or the bf16 [2 E, H] tensor of ``split_router`` (tensor cores).
 
     ``mode="softmax"``: the softmax top-k of ``route``.  ``mode="sigmoid"``: the reference layer's router
     (muse_decode_layer/reference.py:419-424): scores = sigmoid(multiplier * logits), ``bias`` f32 [E] is
@@ -329,7 +344,10 @@ def route_hidden(hidden_states: torch.Tensor, router_w: torch.Tensor, state: dic
     plan: MoEPlan = state["plan"]
     hidden, stride = _check_hidden(hidden_states, plan)
     _need_cuda(router_w, bias)
-    if router_w.dtype != torch.float32 or tuple(router_w.shape) != (plan.n_experts, plan.hidden):
+    split = router_w.dtype == torch.bfloat16
+    if split and tuple(router_w.shape) != (2 * plan.n_experts, plan.hidden):
+        raise ValueError(f"a split router matrix must be bf16 [{2 * plan.n_experts}, {plan.hidden}]")
+    if not split and (router_w.dtype != torch.float32 or tuple(router_w.shape) != (plan.n_experts, plan.hidden)):
         raise ValueError(f"router_w must be f32 [{plan.n_experts}, {plan.hidden}]")
     if bias is not None and (bias.dtype != torch.float32 or tuple(bias.shape) != (plan.n_experts,)):
         raise ValueError(f"bias must be f32 [{plan.n_experts}]")
@@ -338,8 +356,9 @@ def route_hidden(hidden_states: torch.Tensor, router_w: torch.Tensor, state: dic
     T = hidden.shape[0]
     t0, t1 = _own(plan, T, own_tokens)
     router_w = router_w.contiguous()
-    r = _lib.Router(w=router_w.data_ptr(), bias=None if bias is None else bias.contiguous().data_ptr(),
-                    mode=0 if mode == "softmax" else 1, multiplier=float(multiplier))
+    r = _lib.Router(w=None if split else router_w.data_ptr(), bias=None if bias is None else bias.contiguous().data_ptr(),
+                    mode=0 if mode == "softmax" else 1, multiplier=float(multiplier),
+                    w_split=router_w.data_ptr() if split else None)
     _lib.check(_lib.lib().okc_moe_route_hidden(C.byref(plan.c_plan()), C.byref(r), hidden.data_ptr(), stride, None, T,
                                                t0, t1, state["ids"].data_ptr(), state["wts"].data_ptr(),
                                                state["workspace"].data_ptr(), _stream()), "okc_moe_route_hidden")

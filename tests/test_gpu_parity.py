@@ -405,12 +405,13 @@ def _near_tie_ok(ids_gpu, ids_ref, key, tol):
     return bool((np.abs(kg - kr)[ids_gpu != ids_ref] <= tol).all())
 
 
+@pytest.mark.parametrize("tensor_cores", [False, True])
 @pytest.mark.parametrize("T,H,E,k,mode", [(32, 4096, 128, 8, "softmax"), (64, 7168, 256, 8, "sigmoid"), (5, 512, 16, 2, "sigmoid"),
                                           (256, 1024, 160, 6, "softmax")])
-def test_route_from_hidden_states_matches_the_layer_router(T, H, E, k, mode):
-    """Router logits computed from the token rows on the GPU (FP32 split-K) + top-k, against the float64
-    logits of the oracle: the reference's tolerance checker passes, ids agree except at near ties, the
-    weights agree, and the sort tables are those of the chosen ids."""
+def test_route_from_hidden_states_matches_the_layer_router(T, H, E, k, mode, tensor_cores):
+    """Router logits computed from the token rows on the GPU (FP32 split-K on CUDA cores, or bf16 hi + lo on the
+    tensor cores) + top-k, against the float64 logits of the oracle: the reference's tolerance checker passes,
+    ids agree except at near ties, the weights agree, and the sort tables are those of the chosen ids."""
     dev = _dev()
     g = torch.Generator(device="cpu").manual_seed(700 + T)
     hidden = torch.randn((T, H), generator=g).to(torch.bfloat16)
@@ -421,7 +422,13 @@ def test_route_from_hidden_states_matches_the_layer_router(T, H, E, k, mode):
     state = {"plan": plan, "workspace": torch.zeros(sz.workspace_bytes, dtype=torch.uint8, device=dev),
              "ids": torch.zeros((plan.max_tokens, k), dtype=torch.int32, device=dev),
              "wts": torch.zeros((plan.max_tokens, k), dtype=torch.float32, device=dev)}
-    ids, wts = okc.route_hidden(hidden.to(dev), router_w.to(dev), state, bias=None if bias is None else bias.to(dev), mode=mode)
+    rw = okc.split_router(router_w.to(dev)) if tensor_cores else router_w.to(dev)
+    if tensor_cores:
+        hi, lo = rw[:E].float().cpu(), rw[E:].float().cpu()
+        assert (hi + lo - router_w).abs().max() <= router_w.abs().max() * 2.0 ** -15      # w = hi + lo to 16 bits or so
+    ids, wts = okc.route_hidden(hidden.to(dev), rw, state, bias=None if bias is None else bias.to(dev), mode=mode)
+    rc, detail = okc.read_status(state)
+    assert rc == 0, f"device status {rc} detail {detail:#x}"
     ids, wts = ids.cpu().numpy(), wts.cpu().numpy()
     hb = hidden.view(torch.uint16).numpy()
     scores, biased, logits = moe_np.router_scores(hb, router_w.numpy(), None if bias is None else bias.numpy())
@@ -766,3 +773,52 @@ def test_pre_expert_norm_in_the_gather_and_f32_rows_out(rows_f32):
     assert torch.equal(out, okc.moe_step(hidden, logits, state, out_f32=True, pre_norm_gain=gain.to(dev)))
     if not rows_f32:
         assert not torch.equal(out, okc.moe_step(hidden, logits, state, out_f32=True))
+
+
+def test_many_routing_shapes_narrow_wide_and_mixed_steps():
+    """Forty steps with random token counts and routing skews on one set of weights: narrow steps, wide steps
+    and steps that mix 16-row narrow items with 32- and 64-row wide ones, one after the other on the same
+    state.  Every step must end with a clean status (no bounded wait ran out: the barrier protocol of the GEMM
+    launch holds whatever the mix), give the same bits twice, and match the oracle."""
+    dev = _dev()
+    base = synth.Workload("mix", 0, 1024, 512, 24, 4)
+    w = synth.make_weights(base, seed=81, device=dev)
+    wn = synth.to_numpy_weights(w)
+    state = okc.prepare(w, okc.MoEPlan(hidden=1024, inter=512, n_experts=24, top_k=4, max_tokens=512))
+    rng = np.random.default_rng(82)
+    kinds = set()
+    for it in range(40):
+        T = int(rng.integers(1, 400))
+        alpha = float(rng.choice([0.0, 0.0, 0.8, 1.5, 3.0]))
+        wl = synth.Workload("mix", T, 1024, 512, 24, 4, zipf_alpha=alpha)
+        hidden, logits = synth.make_inputs(wl, seed=1000 + it, device=dev)
+        out = okc.moe_step(hidden, logits, state)
+        rc, detail = okc.read_status(state)
+        assert rc == 0, f"step {it} (T={T}, alpha={alpha}): device status {rc} detail {detail:#x}"
+        pads = set(okc.sorted_routes(state, T)["items"][:, 3].tolist())
+        kinds.add("wide" if 64 in pads else "narrow")      # a wide step's heaviest expert has an item padded to 64 rows
+        assert torch.equal(out, okc.moe_step(hidden, logits, state)), f"step {it}: not deterministic"
+        if it % 4 == 0:
+            sub = sorted({0, T // 2, T - 1})
+            _, ref, ids, _ = moe_np.moe_step(_bits(hidden)[sub], logits.cpu().numpy()[sub], wn, 4)
+            _check_out(out[sub], ref, f"step {it} (T={T}, alpha={alpha})")
+    assert kinds == {"narrow", "wide"}
+
+
+def test_prefill_size_step():
+    """A step far beyond decode sizes: 1536 tokens, 6144 routes over 16 experts (384 rows per expert, wide
+    items of 64 rows, N = 64 MMAs), the regime where the contraction is dense.  Oracle on six tokens."""
+    dev = _dev()
+    wl = synth.Workload("prefill", 1536, 2048, 1024, 16, 4)
+    w = synth.make_weights(wl, seed=91, device=dev)
+    state = okc.prepare(w, okc.MoEPlan(hidden=2048, inter=1024, n_experts=16, top_k=4, max_tokens=1536))
+    hidden, logits = synth.make_inputs(wl, seed=92, device=dev)
+    out = okc.moe_step(hidden, logits, state)
+    _status_ok(state)
+    items = okc.sorted_routes(state, 1536)["items"].cpu().numpy()
+    assert (items[:, 3] == 64).sum() >= 80 and int(okc.sorted_routes(state, 1536)["counts"].max()) > 300
+    sub = [0, 1, 511, 777, 1024, 1535]
+    _, ref, ids, _ = moe_np.moe_step(_bits(hidden)[sub], logits.cpu().numpy()[sub], synth.to_numpy_weights(w), 4)
+    assert np.array_equal(state["ids"][:1536].cpu().numpy()[sub], ids)
+    _check_out(out[sub], ref, "prefill-size step")
+    assert torch.equal(out, okc.moe_step(hidden, logits, state))
