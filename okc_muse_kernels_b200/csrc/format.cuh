@@ -80,6 +80,7 @@ constexpr uint32_t kLeftMask = 0x60306030u;    // bits of w0 its three rotations
 enum MetaWord { kMetaItems = 0, kMetaLocalRoutes = 1, kMetaStatus = 2, kMetaDetail = 3, kMetaTokens = 4,
                 kMetaWcap = 5,       // rows of the step's widest work item, padded: 16, 32 or 64 (64: a wide step)
                 kMetaRouterStatus = 6,   // set by the router-logits kernel when one of its waits ran out; the sort takes it over
+                kMetaRouteTicket = 7,    // CTAs of the routing kernel that are done; the last one sorts and puts it back to zero
                 kMetaWorkFused = 8, kMetaWorkPhase0 = 9, kMetaWorkPhase1 = 10,   // unit counters of the GEMM launches
                 kMetaWords = 64 };
 

@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(256) okc_router_partial(const uint16_t* __rest
                                                           float* __restrict__ part) {
   __shared__ uint32_t hs[kRtMaxT][kRtK / 2 + 1];   // bf16 pairs, rows padded against bank conflicts
   __shared__ __align__(16) float ws[kRtE][kRtK + 2]; // even row stride: a thread reads k pairs as 8 bytes
+  griddep_launch_dependents();   // the top-k kernel may set itself up; it waits for this grid to complete
   // thread = experts e0 + 2 eg, + 1 and tokens tg + 32 j
   const int tid = threadIdx.x, eg = tid & 7, tg = tid >> 3;
   const int e0 = blockIdx.x * kRtE;
@@ -99,34 +100,9 @@ __global__ void __launch_bounds__(256) okc_router_partial(const uint16_t* __rest
   }
 }
 
-// Top-k of the router, one warp per token, eight tokens per CTA (the tokens of a step spread over
-// many SMs: one CTA doing all of them is bound by its own instruction issue).
-// PER = candidates per lane (expert e sits in lane e % 32, slot e / 32).  Every lane keeps the best
-// of its untaken candidates; a round is a warp arg-max over those 32 values, after which only the
-// winner's lane looks for its next best.  Order: larger key first, ties to the lower expert id,
-// NaN never wins.
-//   mode 0 (softmax):  key = logit; weights = softmax over the k selected logits.
-//   mode 1 (sigmoid):  score = sigmoid(mult * logit), key = score + bias[e]; weights = the selected
-//                      scores over (their sum + 1e-15)   (muse_decode_layer/reference.py:419-424,
-//                      variants/starter.py:177-182).
-// The logits are read from `logits` [T, E], or, with n_part > 0, as the sum in split order of the
-// n_part arrays [T, E] behind `logits` (the output of okc_router_partial).
-template <int PER>
-__global__ void __launch_bounds__(256) okc_route_topk(const float* __restrict__ logits, int n_part, int T, int E, int k,
-                                                      int mode, float mult, const float* __restrict__ bias,
-                                                      int32_t* __restrict__ ids_out, float* __restrict__ wts_out) {
-  griddep_wait();                // with n_part > 0 the logits come from the kernel launched just before
-  griddep_launch_dependents();   // the sort kernel may set itself up; it waits for this grid to complete
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (t >= T) return;
-  topk_token<PER>(logits + static_cast<size_t>(t) * E, n_part, static_cast<size_t>(T) * E, E, k, mode, mult, bias, lane,
-                  ids_out + t * k, wts_out + t * k);
-}
-
 // Router and sort of a small step in one CTA (T <= 32: a warp per token does the top-k, then all warps
-// sort): one launch and its gap fewer than okc_route_topk + okc_route_sort, which is what a step of a few
-// tokens is made of.  Beyond 32 tokens the top-k of all tokens on one SM costs more than the launch.
+// sort), for logits that are given.  Beyond 32 tokens, or when the logits are split-K partial sums, the top-k of
+// all tokens on one SM costs more than spreading them (okc_route_topk_sort_grid).
 template <int PER>
 __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_topk_sort(const RouteParams p, const float* __restrict__ logits,
                                                                        int n_part) {
@@ -138,6 +114,53 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_route_topk_sort(const Ro
                     p.router_mult, p.router_bias, lane, p.ids_out + warp * p.k, p.wts_out + warp * p.k);
   __threadfence();
   __syncthreads();
+  sort_routes_cta<kRouteThreads>(p, sm);
+}
+
+// Router and sort of any step in one launch: CTA x does the top-k of tokens [x * per_cta, (x + 1) * per_cta), a warp
+// per token, and the CTA that finishes last (a ticket in the control words, which it puts back to zero) sorts the
+// whole step.  The tokens spread over the SMs -- what matters when every token's logits are the sum of many
+// split-K partial arrays, or when there are hundreds of tokens -- and the sort needs no launch of its own.
+template <int PER>
+__global__ void __launch_bounds__(kRouteThreads, 1) okc_route_topk_sort_grid(const RouteParams p, const float* __restrict__ logits,
+                                                                            int n_part, int per_cta, int stage_parts) {
+  extern __shared__ int32_t sm[];
+  __shared__ int s_last;
+  griddep_wait();
+  griddep_launch_dependents();   // the gather kernel may set itself up; it waits for this grid to complete
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (stage_parts) {
+    // one token per CTA: all warps fetch the token's partial rows at once, the sums are formed in split order
+    float* stage = reinterpret_cast<float*>(sm);     // [n_part][E]
+    const int t = blockIdx.x, ev = p.E / 4;
+    const float* first = logits + static_cast<size_t>(t) * p.E;
+    for (int i = threadIdx.x; i < n_part * ev; i += blockDim.x) {
+      const int s = i / ev, c = i - s * ev;
+      reinterpret_cast<float4*>(stage)[i] = __ldcg(reinterpret_cast<const float4*>(first + static_cast<size_t>(s) * p.T * p.E) + c);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+      float x = stage[e];
+      for (int s = 1; s < n_part; ++s) x += stage[s * p.E + e];
+      stage[e] = x;
+    }
+    __syncthreads();
+    if (warp == 0)
+      topk_token<PER>(stage, 1, 0, p.E, p.k, p.router_mode, p.router_mult, p.router_bias, lane, p.ids_out + t * p.k,
+                      p.wts_out + t * p.k);
+  } else {
+    const int t = blockIdx.x * per_cta + warp;
+    if (warp < per_cta && t < p.T)
+      topk_token<PER>(logits + static_cast<size_t>(t) * p.E, n_part, static_cast<size_t>(p.T) * p.E, p.E, p.k, p.router_mode,
+                      p.router_mult, p.router_bias, lane, p.ids_out + t * p.k, p.wts_out + t * p.k);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&p.meta[kMetaRouteTicket], 1) == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x == 0) p.meta[kMetaRouteTicket] = 0;
   sort_routes_cta<kRouteThreads>(p, sm);
 }
 
@@ -298,36 +321,40 @@ cudaError_t launch_route(const RouteParams& p, cudaStream_t stream) {
       if (e != cudaSuccess) return e;
       lg = p.router_part;
     }
-    if (p.T <= kRouteThreads / 32) {
-      // a small step: top-k and sort in one CTA
-      RouteParams q = p;
-      q.logits = nullptr; q.router_w = nullptr; q.router_w_split = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
-      const dim3 one(1), threads(kRouteThreads);
+    RouteParams q = p;
+    q.logits = nullptr; q.router_w = nullptr; q.router_w_split = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
+    const dim3 threads(kRouteThreads);
+    if (n_part == 0 && p.T <= kRouteThreads / 32) {
+      // a small step with its logits given: top-k and sort in one CTA
+      const dim3 one(1);
       if (p.E <= 128) {
         e = cudaFuncSetAttribute(okc_route_topk_sort<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<4>, one, threads, smem, stream, n_part > 0, q, lg, n_part);
+        return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<4>, one, threads, smem, stream, false, q, lg, n_part);
       }
       if (p.E <= 256) {
         e = cudaFuncSetAttribute(okc_route_topk_sort<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<8>, one, threads, smem, stream, n_part > 0, q, lg, n_part);
+        return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<8>, one, threads, smem, stream, false, q, lg, n_part);
       }
       e = cudaFuncSetAttribute(okc_route_topk_sort<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<16>, one, threads, smem, stream, n_part > 0, q, lg, n_part);
+      return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort<16>, one, threads, smem, stream, false, q, lg, n_part);
     }
-    const dim3 grid((p.T + 7) / 8), block(256);
-    if (p.E <= 128)
-      e = launch_kernel(okc_route_topk<4>, grid, block, 0, stream, n_part > 0, lg, n_part, p.T, p.E, p.k, p.router_mode,
-                        p.router_mult, p.router_bias, p.ids_out, p.wts_out);
-    else if (p.E <= 256)
-      e = launch_kernel(okc_route_topk<8>, grid, block, 0, stream, n_part > 0, lg, n_part, p.T, p.E, p.k, p.router_mode,
-                        p.router_mult, p.router_bias, p.ids_out, p.wts_out);
-    else
-      e = launch_kernel(okc_route_topk<16>, grid, block, 0, stream, n_part > 0, lg, n_part, p.T, p.E, p.k, p.router_mode,
-                        p.router_mult, p.router_bias, p.ids_out, p.wts_out);
-    if (e != cudaSuccess) return e;
-    RouteParams q = p;
-    q.logits = nullptr; q.router_w = nullptr; q.router_w_split = nullptr; q.ids_in = p.ids_out; q.wts_in = p.wts_out;
-    return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, q);
+    // the tokens over many SMs, the last CTA sorts.  Split-K partial sums: a CTA per token, the partial rows staged
+    // in shared memory when they fit.
+    const size_t stage_bytes = static_cast<size_t>(n_part) * p.E * sizeof(float);
+    const int stage_parts = (n_part > 1 && (p.E % 4) == 0 && stage_bytes <= 160 * 1024) ? 1 : 0;
+    const int per_cta = stage_parts ? 1 : (p.T <= 64 ? 4 : 8);
+    const size_t smem_g = stage_parts && stage_bytes > smem ? stage_bytes : smem;
+    const dim3 grid((p.T + per_cta - 1) / per_cta);
+    if (p.E <= 128) {
+      e = cudaFuncSetAttribute(okc_route_topk_sort_grid<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_g));
+      return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort_grid<4>, grid, threads, smem_g, stream, n_part > 0, q, lg, n_part, per_cta, stage_parts);
+    }
+    if (p.E <= 256) {
+      e = cudaFuncSetAttribute(okc_route_topk_sort_grid<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_g));
+      return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort_grid<8>, grid, threads, smem_g, stream, n_part > 0, q, lg, n_part, per_cta, stage_parts);
+    }
+    e = cudaFuncSetAttribute(okc_route_topk_sort_grid<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_g));
+    return e != cudaSuccess ? e : launch_kernel(okc_route_topk_sort_grid<16>, grid, threads, smem_g, stream, n_part > 0, q, lg, n_part, per_cta, stage_parts);
   }
   return launch_kernel(okc_route_sort, dim3(1), dim3(kRouteThreads), smem, stream, true, p);
 }

@@ -38,6 +38,7 @@ struct RouterMmaParams {
 
 __global__ void __launch_bounds__(128) okc_router_mma(const __grid_constant__ RouterMmaParams p) {
   extern __shared__ uint8_t smem_raw[];
+  griddep_launch_dependents();   // the top-k kernel may set itself up; it waits for this grid to complete
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   __shared__ uint64_t bar_full[kRmMaxKb];
   __shared__ uint64_t bar_done;
