@@ -58,7 +58,8 @@ typedef struct okc_moe_plan {
 typedef struct okc_moe_sizes {
   uint64_t packed_w13_bytes;   /* repacked w13 of (local_count + shared) experts */
   uint64_t packed_w2_bytes;    /* repacked w2 of the same experts */
-  uint64_t workspace_bytes;    /* scratch for one step in flight */
+  uint64_t workspace_bytes;    /* scratch for one step in flight; zeroed once by the caller before its first step
+                                  (the control words at its start count and hand over between kernels) */
   uint32_t expert_slots;       /* local_count + (shared_inter ? 1 : 0) */
   uint32_t routes_per_token;   /* top_k + (shared_inter ? 1 : 0) */
 } okc_moe_sizes;

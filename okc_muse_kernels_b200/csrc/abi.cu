@@ -287,11 +287,17 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   Ws w = carve(workspace, g);
   const int R = T * g.kk;
 
+  // A step of a few tokens needs no gathered copy of its rows: the GEMM's producer fetches each row of a work item
+  // from `hidden` itself.  Larger steps (items of up to 64 rows: one boxed copy instead of 64) and steps with the
+  // pre-expert norm go through the gather kernel.
+  const bool direct = pre == nullptr && T <= kDirectRowsMaxTokens;
   if (ev && cudaEventRecord(ev[0], stream) != cudaSuccess) return OKC_ERR_CUDA;
-  const cudaError_t ge = pre ? launch_gather_norm(hidden, hidden_stride, pre->hidden_f32, pre->gain, pre->eps, w.meta, w.sorted,
-                                                  g.kk, g.H, R, w.xg, w.done, g.max_items, stream)
-                             : launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, w.done, g.max_items, stream);
-  if (ge != cudaSuccess) return OKC_ERR_CUDA;
+  if (!direct) {
+    const cudaError_t ge = pre ? launch_gather_norm(hidden, hidden_stride, pre->hidden_f32, pre->gain, pre->eps, w.meta, w.sorted,
+                                                    g.kk, g.H, R, w.xg, w.done, g.max_items, stream)
+                               : launch_gather(hidden, hidden_stride, w.meta, w.sorted, g.kk, g.H, R, w.xg, w.done, g.max_items, stream);
+    if (ge != cudaSuccess) return OKC_ERR_CUDA;
+  }
   if (ev && cudaEventRecord(ev[1], stream) != cudaSuccess) return OKC_ERR_CUDA;
 
   // Both GEMM phases in one persistent launch: gate_up units first, then down units, each down
@@ -310,6 +316,13 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   a.meta = w.meta; a.items = w.items; a.done = w.done;
   a.inter = w.inter; a.I = g.I; a.H = g.H; a.y = w.y; a.sorted = w.sorted; a.wsorted = w.wsorted;
   a.weighted = plan->post_norm ? 0 : 1;
+  a.kk = g.kk; a.max_items = g.max_items;
+  if (direct) {
+    a.direct_rows = 1;
+    if (!encode_rows_map(&a.hmap, const_cast<void*>(hidden), static_cast<uint64_t>(T), static_cast<uint64_t>(g.H), 1,
+                         static_cast<uint64_t>(hidden_stride)))
+      return OKC_ERR_CUDA;
+  }
   a.phase_lo = 0; a.phase_hi = 1; a.work_counter = w.meta + kMetaWorkFused;
   if (launch_gemm(a, sms, stream) != cudaSuccess) return OKC_ERR_CUDA;
   if (ev && cudaEventRecord(ev[2], stream) != cudaSuccess) return OKC_ERR_CUDA;

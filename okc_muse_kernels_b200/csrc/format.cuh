@@ -62,6 +62,9 @@ __host__ __device__ inline bool wide_step_pays(int cmax, long long items_narrow,
 // beyond, half a stage (18 KB of weights + wcap token rows of 128 K elements).
 constexpr int kSmemBudget = 232448;
 constexpr int kGemmCtrlReserve = 2048;
+// Steps of up to this many tokens read their token rows straight from the caller's array (an item then has at most
+// this many rows: a token sends at most one route to an expert).
+constexpr int kDirectRowsMaxTokens = 8;
 constexpr int kMaxStages = 6;
 __host__ __device__ inline int gemm_slot_bytes(int wcap) {
   return wcap > kNarrowRows ? 36864 / 2 + wcap * 256 : 36864 + wcap * 512;
@@ -82,6 +85,7 @@ enum MetaWord { kMetaItems = 0, kMetaLocalRoutes = 1, kMetaStatus = 2, kMetaDeta
                 kMetaRouterStatus = 6,   // set by the router-logits kernel when one of its waits ran out; the sort takes it over
                 kMetaRouteTicket = 7,    // CTAs of the routing kernel that are done; the last one sorts and puts it back to zero
                 kMetaWorkFused = 8, kMetaWorkPhase0 = 9, kMetaWorkPhase1 = 10,   // unit counters of the GEMM launches
+                kMetaGemmExit = 11,      // CTAs of the GEMM launch that are through; the last one clears the per-call counters
                 kMetaWords = 64 };
 
 struct Geometry {

@@ -110,6 +110,7 @@ struct Ctrl {
   UnitDesc units[kURing];
   uint32_t tmem_base;
   int abort_code;
+  int last_out;
 };
 
 // Next unit descriptor for a consumer role: waits until the producer published ring entry
@@ -206,14 +207,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      for (int ph = 0; ph < 2; ++ph)
-        for (int i = 0; i < 5; ++i) tma_prefetch_desc(&p.ph[ph].bmap[i]);
+    // The whole warp runs the loop (the waits and the decisions are the same in every lane); lane 0 takes the
+    // units, publishes them and starts the weight copies, and the token copies of a ring slot are spread over
+    // the lanes: a thread that starts a dozen copies per stage one after the other is slower than the stage.
+    // (The outcome of every wait is made the same in all lanes by a vote, so that the shuffles below always
+    // find the whole warp.)
+    {
+      if (lane == 0) {
+        for (int ph = 0; ph < 2; ++ph)
+          for (int i = 0; i < 5; ++i) tma_prefetch_desc(&p.ph[ph].bmap[i]);
+        if (p.direct_rows) tma_prefetch_desc(&p.hmap);
+      }
       const uint64_t pol = policy_evict_first();
       const int n_items = p.meta[kMetaItems];
       const int units0 = n_items * p.ph[0].pairs, units1 = n_items * p.ph[1].pairs;
       const int first = (p.phase_lo == 0) ? 0 : units0;
       const int last = (p.phase_hi == 1) ? units0 + units1 : units0;
+      const int nkb = half ? 2 : 4;                                // 64-element blocks of token rows per ring slot
+      const uint32_t tok_off = half ? kHalfStageBytes : kStageBytes;
       int st = 0;
       uint32_t ph = 0;
       int issued = 0;
@@ -221,13 +232,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
       OKC_PROF_DECL
       for (uint32_t n = 0; ok; ++n) {
         const uint32_t k = n % kURing;
-        if (!mbar_wait<200>(bar_uempty + 8 * k, ((n / kURing) & 1) ^ 1, abort_flag, kWaitProducerUnit)) { ok = false; break; }
-        const int g = first + atomicAdd(p.work_counter, 1);
+        if (!__all_sync(0xffffffffu, mbar_wait<200>(bar_uempty + 8 * k, ((n / kURing) & 1) ^ 1, abort_flag, kWaitProducerUnit))) { ok = false; break; }
+        int g0 = 0;
+        if (lane == 0) g0 = atomicAdd(p.work_counter, 1);
+        const int g = first + __shfl_sync(0xffffffffu, g0, 0);
         UnitDesc u;
         if (g >= last) {
           u.phase = -1; u.slot = 0; u.pos0 = 0; u.rows = 0; u.npad = 16; u.pair = 0; u.item = 0; u.stages = 0;
-          ctrl->units[k] = u;
-          mbar_arrive(bar_ufull + 8 * k);
+          if (lane == 0) {
+            ctrl->units[k] = u;
+            mbar_arrive(bar_ufull + 8 * k);
+          }
           break;
         }
         u.phase = (g < units0) ? 0 : 1;
@@ -243,27 +258,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
         // otherwise be a sixth of all bytes the SM takes in.
         const int mi = (u.rows <= 4) ? 0 : (u.rows <= 8) ? 1 : (u.rows <= 16) ? 2 : (u.rows <= 32) ? 3 : 4;
         const int brows = 4 << mi;                               // token rows copied per stage
-        ctrl->units[k] = u;
-        mbar_arrive(bar_ufull + 8 * k);
+        if (lane == 0) {
+          ctrl->units[k] = u;
+          mbar_arrive(bar_ufull + 8 * k);
+        }
         const uint8_t* src = pp.wpacked + static_cast<size_t>(u.slot) * pp.expert_bytes +
                              static_cast<size_t>(u.pair) * pp.stages * kStageBytes;
         const int steps = pp.stages * sps;                       // ring slots this unit goes through
-        const uint32_t tx_bytes = half ? kHalfStageBytes + brows * 256 : kStageBytes + brows * 512;
-        // weights of ring step r of the unit -> slot at dst
+        // gate_up units of a small step take their rows from the caller's array, row by row: lane j knows
+        // the token of row j
+        const bool direct = p.direct_rows != 0 && u.phase == 0;
+        int my_tok = 0;
+        if (direct && lane < u.rows) my_tok = p.sorted[u.pos0 + lane] / p.kk;
+        const int crows = direct ? u.rows : brows;               // token rows that arrive per ring slot
+        const int n_ops = crows * nkb;                           // direct: row copies per ring slot
+        const uint32_t tx_bytes = tok_off + crows * nkb * 128;
+        // weights of ring step r of the unit -> slot at dst (lane 0)
         auto send_weights = [&](int r, uint32_t dst, uint32_t bar) {
-          if (!half) bulk_g2s_hint(dst, src + static_cast<size_t>(r) * kStageBytes, kStageBytes, bar, pol);
-          else bulk_g2s_hint(dst, src + static_cast<size_t>(r) * kHalfStageBytes, kHalfStageBytes, bar, pol);
+          if (lane == 0) bulk_g2s_hint(dst, src + static_cast<size_t>(r) * tok_off, tok_off, bar, pol);
         };
-        // token rows of ring step r -> behind the weights of the slot
+        // token rows of ring step r -> behind the weights of the slot (all lanes)
         auto send_tokens = [&](int r, uint32_t dst, uint32_t bar) {
-          if (!half) {
-#pragma unroll
-            for (int kb = 0; kb < 4; ++kb)
-              tma_2d_g2s(dst + kStageBytes + kb * u.npad * 128, &pp.bmap[mi], r * kStageK + kb * 64, u.pos0, bar);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-              tma_2d_g2s(dst + kHalfStageBytes + j * u.npad * 128, &pp.bmap[mi], (r >> 1) * kStageK + ((r & 1) * 2 + j) * 64, u.pos0, bar);
+          const int k0 = half ? (r >> 1) * kStageK + (r & 1) * 128 : r * kStageK;
+          const uint32_t base = dst + tok_off;
+          if (direct) {
+            // (the 128-byte swizzle is a function of the shared-memory address, so single rows land where a box
+            // of rows would have put them)
+            for (int o0 = 0; o0 < n_ops; o0 += 32) {
+              const int o = o0 + lane;
+              const int row = half ? (o >> 1) : (o >> 2), kb = half ? (o & 1) : (o & 3);
+              const int t = __shfl_sync(0xffffffffu, my_tok, row & 31);
+              if (o < n_ops) tma_2d_g2s(base + kb * u.npad * 128 + row * 128, &p.hmap, k0 + kb * 64, t, bar);
+            }
+          } else if (lane < nkb) {
+            tma_2d_g2s(base + lane * u.npad * 128, &pp.bmap[mi], k0 + lane * 64, u.pos0, bar);
           }
         };
         int r_begin = 0;
@@ -279,8 +307,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
             int st2 = st, sent = 0;
             uint32_t ph2 = ph;
             for (int r = 0; r < pre; ++r) {
-              if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st2, ph2 ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
-              mbar_expect_tx(bar_full + 8 * st2, tx_bytes);
+              if (!__all_sync(0xffffffffu, OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st2, ph2 ^ 1, abort_flag, kWaitProducerEmpty)))) { ok = false; break; }
+              if (lane == 0) mbar_expect_tx(bar_full + 8 * st2, tx_bytes);
               send_weights(r, smem0 + st2 * slot_bytes, bar_full + 8 * st2);
               ++sent;
               if (++st2 == NS) { st2 = 0; ph2 ^= 1; }
@@ -293,6 +321,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
                 if (spins >= (1u << 22)) { atomicCAS(const_cast<int*>(abort_flag), 0, kWaitProducerDone); ok = false; break; }
               }
             }
+            ok = __all_sync(0xffffffffu, ok);
             fence_proxy_async();   // those stores were generic-proxy writes; the loads below are TMA
             // (also when giving up: the slots whose weights are in flight get their token tiles, so
             // that their barriers complete and the CTA can wait for its copies before it retires)
@@ -308,18 +337,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
           }
         }
         for (int r = r_begin; r < steps; ++r) {
-          if (!OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty))) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, OKC_PROF_WAIT(1, mbar_wait<500>(bar_empty + 8 * st, ph ^ 1, abort_flag, kWaitProducerEmpty)))) { ok = false; break; }
           const uint32_t bar = bar_full + 8 * st;
           const uint32_t dst = smem0 + st * slot_bytes;
-          mbar_expect_tx(bar, tx_bytes);
+          if (lane == 0) mbar_expect_tx(bar, tx_bytes);
           send_weights(r, dst, bar);
           send_tokens(r, dst, bar);
           ++issued;
           if (++st == NS) { st = 0; ph ^= 1; }
         }
       }
-      OKC_PROF_STORE(0, 0, 1)
-      if (!ok) {
+      if (lane == 0) { OKC_PROF_STORE(0, 0, 1) }
+      if (!ok && lane == 0) {
         // give copies already issued a bounded chance to land before the CTA retires
         const int n = issued < NS ? issued : NS;
         for (int j = 0; j < n; ++j) {
@@ -656,9 +685,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
-  if (tid == 0 && ctrl->abort_code != 0) {
-    atomicCAS(const_cast<int32_t*>(&p.meta[kMetaStatus]), 0, OKC_ERR_TIMEOUT);
-    atomicCAS(const_cast<int32_t*>(&p.meta[kMetaDetail]), 0, ((p.phase_lo * 2 + p.phase_hi) << 8) | ctrl->abort_code);
+  int32_t* meta = const_cast<int32_t*>(p.meta);
+  if (tid == 0) {
+    if (ctrl->abort_code != 0) {
+      atomicCAS(&meta[kMetaStatus], 0, OKC_ERR_TIMEOUT);
+      atomicCAS(&meta[kMetaDetail], 0, ((p.phase_lo * 2 + p.phase_hi) << 8) | ctrl->abort_code);
+    }
+    // The CTA that leaves last puts the per-call state back to zero: the unit counters and the per-item
+    // completion counts, so that the next launch on this workspace needs no kernel in front of it to do so.
+    __threadfence();
+    ctrl->last_out = (p.phase_hi == 1 && atomicAdd(&meta[kMetaGemmExit], 1) == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (ctrl->last_out) {
+    for (int i = tid; i < p.max_items; i += blockDim.x) p.done[i] = 0;
+    if (tid < 3) meta[kMetaWorkFused + tid] = 0;
+    if (tid == 3) meta[kMetaGemmExit] = 0;
   }
 }
 

@@ -87,6 +87,12 @@ struct MoeGemmParams {
   const float* wsorted;
   int H;
   int weighted;
+  // Token rows of the gate_up phase taken straight from the caller's `hidden` (no gathered copy): one TMA copy
+  // per row and 64-element block, the row being the token of the route at that sorted position.
+  int direct_rows;
+  int kk;                     // routes per token: token of sorted entry s = s / kk
+  int max_items;
+  CUtensorMap hmap;           // hidden [T, H] bf16 with the caller's row stride, box = 64 elements x 1 row
 };
 cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream);
 
