@@ -34,6 +34,7 @@
 #include <cstdint>
 
 #include "../../include/okc_moe.h"
+#include "combine_device.cuh"
 #include "route_device.cuh"
 
 namespace okc {
@@ -194,13 +195,7 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
   const bool live = col < p.H;
 
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (live) {
-    for (int s = 0; s < c.kk; ++s) {
-      if (c.pos[t * c.kk + s] < 0) continue;   // uniform over the block
-      const float4 a = *reinterpret_cast<const float4*>(c.y + static_cast<size_t>(t * c.kk + s) * p.H + col);
-      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
-    }
-  }
+  if (live) acc = sum_token_routes(c.y, c.pos, t, c.kk, p.H, col);
   if (!own) {
     if (live)
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(mine + p.off_partial) + static_cast<size_t>(t) * p.H + col) = acc;

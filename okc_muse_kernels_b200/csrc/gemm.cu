@@ -37,6 +37,7 @@
 
 #include <type_traits>
 
+#include "combine_device.cuh"
 #include "params.cuh"
 
 namespace okc {
@@ -841,12 +842,7 @@ __global__ void __launch_bounds__(kCombineThreads) okc_combine_sliced(const Comb
   const int t = blockIdx.x;
   const int v = blockIdx.y * kCombineThreads + threadIdx.x;   // float4 index within the row
   if (v >= p.H / 4) return;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < p.kk; ++s) {
-    if (p.pos[t * p.kk + s] < 0) continue;
-    const float4 a = reinterpret_cast<const float4*>(p.y + static_cast<size_t>(t * p.kk + s) * p.H)[v];
-    acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
-  }
+  const float4 acc = sum_token_routes(p.y, p.pos, t, p.kk, p.H, v * 4);
   if (p.out_f32) {
     reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(t) * p.H)[v] = acc;
   } else {
