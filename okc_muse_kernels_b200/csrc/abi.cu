@@ -316,7 +316,7 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   a.meta = w.meta; a.items = w.items; a.done = w.done;
   a.inter = w.inter; a.I = g.I; a.H = g.H; a.y = w.y; a.sorted = w.sorted; a.wsorted = w.wsorted;
   a.weighted = plan->post_norm ? 0 : 1;
-  a.kk = g.kk; a.max_items = g.max_items;
+  a.kk = g.kk;
   if (direct) {
     a.direct_rows = 1;
     if (!encode_rows_map(&a.hmap, const_cast<void*>(hidden), static_cast<uint64_t>(T), static_cast<uint64_t>(g.H), 1,
@@ -330,6 +330,7 @@ static int experts_impl(const okc_moe_plan* plan, const void* packed_w13, const 
   CombineParams c;
   c.y = w.y; c.pos = w.pos; c.wsorted = w.wsorted; c.post_w = static_cast<const uint16_t*>(post_norm_w);
   c.out = out; c.kk = g.kk; c.H = g.H; c.out_f32 = out_f32 ? 1 : 0;
+  c.meta = w.meta; c.done = w.done; c.max_items = g.max_items;
   if (ep) {
     // the combine and the reduce-scatter over the ranks in one kernel
     if (launch_ep_combine_reduce(*ep, c, stream) != cudaSuccess) return OKC_ERR_CUDA;

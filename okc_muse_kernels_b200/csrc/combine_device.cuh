@@ -4,7 +4,19 @@
 
 #include <cstdint>
 
+#include "params.cuh"
+
 namespace okc {
+
+// The combine kernels run behind every GEMM launch; their first CTA puts the per-call state of that launch back to
+// zero (its unit counter and the per-item completion counts), so that the next GEMM launch on this workspace needs no
+// kernel in front of it to do so.
+__device__ __forceinline__ void clear_call_state(const CombineParams& p) {
+  if (blockIdx.x == 0 && blockIdx.y == 0) {
+    for (int i = threadIdx.x; i < p.max_items; i += blockDim.x) p.done[i] = 0;
+    if (threadIdx.x < 3) p.meta[kMetaWorkFused + threadIdx.x] = 0;
+  }
+}
 
 // acc = sum over slots s = 0 .. kk-1 with pos[t * kk + s] >= 0, in slot order, of the four floats at column `col`
 // of y[t * kk + s].  The positions of eight slots and then their rows are all requested before the first add: taken

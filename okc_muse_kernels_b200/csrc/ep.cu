@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(256) okc_ep_pull_reduce(const EpParams p) {
 // advance the step count (every CTA has read it by then).
 __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, const CombineParams c) {
   griddep_wait();    // y comes from the GEMM launch before
+  clear_call_state(c);
   uint8_t* mine = p.peer[p.rank];
   int32_t* ctrl = ctrl_of(mine);
   const int tb = p.tokens / p.world;

@@ -85,7 +85,6 @@ enum MetaWord { kMetaItems = 0, kMetaLocalRoutes = 1, kMetaStatus = 2, kMetaDeta
                 kMetaRouterStatus = 6,   // set by the router-logits kernel when one of its waits ran out; the sort takes it over
                 kMetaRouteTicket = 7,    // CTAs of the routing kernel that are done; the last one sorts and puts it back to zero
                 kMetaWorkFused = 8, kMetaWorkPhase0 = 9, kMetaWorkPhase1 = 10,   // unit counters of the GEMM launches
-                kMetaGemmExit = 11,      // CTAs of the GEMM launch that are through; the last one clears the per-call counters
                 kMetaWords = 64 };
 
 struct Geometry {

@@ -111,7 +111,6 @@ struct Ctrl {
   UnitDesc units[kURing];
   uint32_t tmem_base;
   int abort_code;
-  int last_out;
 };
 
 // Next unit descriptor for a consumer role: waits until the producer published ring entry
@@ -234,9 +233,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
       for (uint32_t n = 0; ok; ++n) {
         const uint32_t k = n % kURing;
         if (!__all_sync(0xffffffffu, mbar_wait<200>(bar_uempty + 8 * k, ((n / kURing) & 1) ^ 1, abort_flag, kWaitProducerUnit))) { ok = false; break; }
-        int g0 = 0;
-        if (lane == 0) g0 = atomicAdd(p.work_counter, 1);
-        const int g = first + __shfl_sync(0xffffffffu, g0, 0);
+        // the first unit of a CTA is the one of its own number (no trip to the counter before the first copy starts);
+        // the counter hands out the units behind those
+        int g0 = static_cast<int>(blockIdx.x);
+        if (n > 0) {
+          if (lane == 0) g0 = static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
+          g0 = __shfl_sync(0xffffffffu, g0, 0);
+        }
+        const int g = first + g0;
         UnitDesc u;
         if (g >= last) {
           u.phase = -1; u.slot = 0; u.pos0 = 0; u.rows = 0; u.npad = 16; u.pair = 0; u.item = 0; u.stages = 0;
@@ -686,22 +690,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) okc_moe_gemm(const __grid_con
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
-  int32_t* meta = const_cast<int32_t*>(p.meta);
-  if (tid == 0) {
-    if (ctrl->abort_code != 0) {
-      atomicCAS(&meta[kMetaStatus], 0, OKC_ERR_TIMEOUT);
-      atomicCAS(&meta[kMetaDetail], 0, ((p.phase_lo * 2 + p.phase_hi) << 8) | ctrl->abort_code);
-    }
-    // The CTA that leaves last puts the per-call state back to zero: the unit counters and the per-item
-    // completion counts, so that the next launch on this workspace needs no kernel in front of it to do so.
-    __threadfence();
-    ctrl->last_out = (p.phase_hi == 1 && atomicAdd(&meta[kMetaGemmExit], 1) == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
-  }
-  __syncthreads();
-  if (ctrl->last_out) {
-    for (int i = tid; i < p.max_items; i += blockDim.x) p.done[i] = 0;
-    if (tid < 3) meta[kMetaWorkFused + tid] = 0;
-    if (tid == 3) meta[kMetaGemmExit] = 0;
+  if (tid == 0 && ctrl->abort_code != 0) {
+    atomicCAS(const_cast<int32_t*>(&p.meta[kMetaStatus]), 0, OKC_ERR_TIMEOUT);
+    atomicCAS(const_cast<int32_t*>(&p.meta[kMetaDetail]), 0, ((p.phase_lo * 2 + p.phase_hi) << 8) | ctrl->abort_code);
   }
 }
 
@@ -714,6 +705,7 @@ constexpr int kCombineMaxPer = 8;   // float4 per thread: H <= 256 * 4 * 8 = 819
 
 __global__ void __launch_bounds__(kCombineThreads) okc_combine(const CombineParams p) {
   griddep_wait();
+  clear_call_state(p);
   const int t = blockIdx.x, tid = threadIdx.x;
   const int nvec = p.H / 4;
   float4 acc[kCombineMaxPer];
@@ -839,6 +831,7 @@ cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream) {
 // from being latency-bound.  Same sums in the same (slot) order as okc_combine.
 __global__ void __launch_bounds__(kCombineThreads) okc_combine_sliced(const CombineParams p) {
   griddep_wait();
+  clear_call_state(p);
   const int t = blockIdx.x;
   const int v = blockIdx.y * kCombineThreads + threadIdx.x;   // float4 index within the row
   if (v >= p.H / 4) return;

@@ -77,7 +77,7 @@ struct MoeGemmParams {
   PhaseParams ph[2];
   const int32_t* meta;
   const int4* items;
-  int32_t* work_counter;      // next unit of this launch (zeroed by the gather kernel)
+  int32_t* work_counter;      // units handed out behind the first grid-size ones (zeroed by the combine kernel of the launch before)
   int32_t* done;              // [items] epilogue warps that finished a gate_up unit of the item
   int phase_lo, phase_hi;
   uint16_t* inter;            // bf16 [Rpad, I]     (phase 0 output, phase 1 token operand)
@@ -91,7 +91,6 @@ struct MoeGemmParams {
   // per row and 64-element block, the row being the token of the route at that sorted position.
   int direct_rows;
   int kk;                     // routes per token: token of sorted entry s = s / kk
-  int max_items;
   CUtensorMap hmap;           // hidden [T, H] bf16 with the caller's row stride, box = 64 elements x 1 row
 };
 cudaError_t launch_gemm(const MoeGemmParams& p, int grid, cudaStream_t stream);
@@ -119,6 +118,9 @@ struct CombineParams {
   const uint16_t* post_w;
   void* out;
   int kk, H, out_f32;
+  int32_t* meta;              // control words and per-item counts of the GEMM launch before: cleared by the first CTA
+  int32_t* done;
+  int max_items;
 };
 cudaError_t launch_combine(const CombineParams& p, int T, cudaStream_t stream);
 cudaError_t launch_ep_combine_reduce(const EpParams& p, const CombineParams& c, cudaStream_t stream);

@@ -185,11 +185,24 @@ __global__ void __launch_bounds__(128) okc_gather_rows(const uint16_t* __restric
     for (int i = threadIdx.x; i < max_items; i += blockDim.x) done[i] = 0;
     if (threadIdx.x < 3) meta[kMetaWorkFused + threadIdx.x] = 0;
   }
-  if (q >= meta[kMetaLocalRoutes]) return;
-  const int t = sorted[q] / kk;
+  // (the count and the route are requested together, and the row's vectors before the first store: the launch is
+  // a chain of dependent trips to L2 otherwise)
+  const int n_local = meta[kMetaLocalRoutes];
+  const int route = sorted[q];
+  if (q >= n_local) return;
+  const int t = route / kk;
   const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * stride);
   uint4* dst = reinterpret_cast<uint4*>(xg + static_cast<size_t>(q) * H);
-  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+  const int nvec = H / 8;
+  for (int i0 = threadIdx.x; i0 < nvec; i0 += 4 * blockDim.x) {
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i0 + j * blockDim.x < nvec) v[j] = src[i0 + j * blockDim.x];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i0 + j * blockDim.x < nvec) dst[i0 + j * blockDim.x] = v[j];
+  }
 }
 
 // The same gather with the pre-expert RMSNorm of the reference's layer applied on the way
