@@ -93,7 +93,7 @@ static void fill_route_params(const okc_moe_plan* plan, const Geometry& g, int T
                               RouteParams& p) {
   Ws w = carve(workspace, g);
   memset(&p, 0, sizeof(p));
-  p.meta = w.meta; p.counts = w.counts; p.items = w.items; p.sorted = w.sorted; p.pos = w.pos; p.wsorted = w.wsorted;
+  p.meta = w.meta; p.counts = w.counts; p.done = w.done; p.items = w.items; p.sorted = w.sorted; p.pos = w.pos; p.wsorted = w.wsorted;
   p.T = T; p.E = plan->n_experts; p.k = plan->top_k; p.kk = g.kk; p.slots = g.slots;
   p.local_start = plan->local_start; p.local_count = plan->local_count; p.has_shared = plan->shared_inter ? 1 : 0;
   p.own_t0 = own_t0; p.own_t1 = own_t1; p.max_items = g.max_items; p.chunk_rows = chunk_rows_for(T, plan->top_k, plan->n_experts);

@@ -14,6 +14,7 @@ struct RouteParams {
   float* wts_out;
   int32_t* meta;
   int32_t* counts;
+  int32_t* done;                  // per-item completion counts of the GEMM launch: the sort leaves them (and the unit counters) at zero
   int4* items;
   int32_t* sorted;
   int32_t* pos;

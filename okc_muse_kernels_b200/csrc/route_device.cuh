@@ -279,6 +279,10 @@ __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* s
     }
   }
   __syncthreads();
+  // the per-call state of the GEMM launch that will work on these routes (the combine kernel behind every GEMM launch
+  // clears it too; a step whose predecessor never got that far starts clean all the same)
+  for (int i = tid; i < p.max_items; i += kThreads) p.done[i] = 0;
+  if (tid < 3) p.meta[kMetaWorkFused + tid] = 0;
   const bool wide_step = s_wide != 0;
   for (int r = tid; r < n_active; r += kThreads) {
     const int e = order[r];
