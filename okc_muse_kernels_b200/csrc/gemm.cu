@@ -711,52 +711,66 @@ __global__ void __launch_bounds__(kCombineThreads) okc_combine(const CombinePara
   float4 acc[kCombineMaxPer];
 #pragma unroll
   for (int i = 0; i < kCombineMaxPer; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  __shared__ float red[kCombineThreads / 32];
-  for (int s = 0; s < p.kk; ++s) {
-    const int q = p.pos[t * p.kk + s];
-    if (q < 0) continue;   // uniform over the block
-    const float4* yr = reinterpret_cast<const float4*>(p.y + static_cast<size_t>(t * p.kk + s) * p.H);
-    if (p.post_w == nullptr) {
+  // (only launched with the post-expert norm; without it okc_combine_sliced runs)
+  // Eight slots at a time, in two passes: the sums of squares of all eight rows first (their loads are all in
+  // flight together and one block-wide reduction serves the eight), then the rows again (from L1 / L2) scaled and
+  // added in slot order.  Slot by slot, every slot cost a trip to L2 and a block-wide reduction of its own.  The
+  // operations on every element, and their order, are the same either way.
+  __shared__ float red[8][kCombineThreads / 32];
+  auto scaled = [&](const float4* yr, int v) {
+    float4 a = yr[v];
+    const uint2 wb = *reinterpret_cast<const uint2*>(p.post_w + v * 4);
+    a.x *= 1.0f + __uint_as_float(wb.x << 16);
+    a.y *= 1.0f + __uint_as_float(wb.x & 0xFFFF0000u);
+    a.z *= 1.0f + __uint_as_float(wb.y << 16);
+    a.w *= 1.0f + __uint_as_float(wb.y & 0xFFFF0000u);
+    return a;
+  };
+  for (int s0 = 0; s0 < p.kk; s0 += 8) {
+    int q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = (s0 + j < p.kk) ? p.pos[t * p.kk + s0 + j] : -1;   // uniform over the block
+    float ss[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ss[j] = 0.f;
+      if (q[j] < 0) continue;
+      const float4* yr = reinterpret_cast<const float4*>(p.y + static_cast<size_t>(t * p.kk + s0 + j) * p.H);
 #pragma unroll
       for (int i = 0; i < kCombineMaxPer; ++i) {
         const int v = tid + i * kCombineThreads;
         if (v < nvec) {
-          const float4 a = yr[v];
-          acc[i].x += a.x; acc[i].y += a.y; acc[i].z += a.z; acc[i].w += a.w;
+          const float4 a = scaled(yr, v);
+          ss[j] += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
         }
       }
-    } else {
-      float4 tmp[kCombineMaxPer];
-      float ss = 0.f;
+    }
 #pragma unroll
-      for (int i = 0; i < kCombineMaxPer; ++i) {
-        const int v = tid + i * kCombineThreads;
-        if (v < nvec) {
-          float4 a = yr[v];
-          const uint2 wb = *reinterpret_cast<const uint2*>(p.post_w + v * 4);
-          a.x *= 1.0f + __uint_as_float(wb.x << 16);
-          a.y *= 1.0f + __uint_as_float(wb.x & 0xFFFF0000u);
-          a.z *= 1.0f + __uint_as_float(wb.y << 16);
-          a.w *= 1.0f + __uint_as_float(wb.y & 0xFFFF0000u);
-          tmp[i] = a;
-          ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-        }
-      }
+    for (int j = 0; j < 8; ++j) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      __syncthreads();
-      if ((tid & 31) == 0) red[tid >> 5] = ss;
-      __syncthreads();
+      for (int o = 16; o > 0; o >>= 1) ss[j] += __shfl_xor_sync(0xffffffffu, ss[j], o);
+    }
+    __syncthreads();
+    if ((tid & 31) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) red[j][tid >> 5] = ss[j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (q[j] < 0) continue;
       float tot = 0.f;
 #pragma unroll
-      for (int i = 0; i < kCombineThreads / 32; ++i) tot += red[i];
-      const float scale = p.wsorted[q] * rsqrtf(tot / static_cast<float>(p.H) + 1e-8f);
+      for (int i = 0; i < kCombineThreads / 32; ++i) tot += red[j][i];
+      const float scale = p.wsorted[q[j]] * rsqrtf(tot / static_cast<float>(p.H) + 1e-8f);
+      const float4* yr = reinterpret_cast<const float4*>(p.y + static_cast<size_t>(t * p.kk + s0 + j) * p.H);
 #pragma unroll
       for (int i = 0; i < kCombineMaxPer; ++i) {
         const int v = tid + i * kCombineThreads;
         if (v < nvec) {
-          acc[i].x += tmp[i].x * scale; acc[i].y += tmp[i].y * scale;
-          acc[i].z += tmp[i].z * scale; acc[i].w += tmp[i].w * scale;
+          const float4 a = scaled(yr, v);
+          acc[i].x += a.x * scale; acc[i].y += a.y * scale;
+          acc[i].z += a.z * scale; acc[i].w += a.w * scale;
         }
       }
     }
