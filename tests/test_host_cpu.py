@@ -216,3 +216,20 @@ def test_oracle_layer_router_and_routing_checker():
     dup = ids.copy()
     dup[1, 1] = dup[1, 0]
     assert "twice" in moe_np.check_routing(dup, biased, k)
+
+
+def test_reference_arm_of_the_bench_runs_on_host_cores():
+    """`bench.py --impl reference` (the oracle on the host cores, no GPU) prints one JSON line with the keys the
+    measurement contract names, on the small configuration."""
+    import json
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "c1",
+                        "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["n_gpus"] == 1 and line["steps"] == 1
+    assert line["value"] > 0 and line["ms_per_step"] > 0 and line["higher_is_better"] is True
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert line["config"]["workload"].startswith("c1")
