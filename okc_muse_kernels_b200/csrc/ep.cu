@@ -248,13 +248,14 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
 }
 
 // push_tokens + top-k of the rank's own tokens + the token -> expert sort of the whole step.
-// grid (row groups, world), 256 threads, dynamic shared memory of route_smem_bytes(R, slots, 256) bytes.
-// CTA (x, r): for rows x, x + gridDim.x, ... of this rank's block, warp 0 routes the row and stores its k
-// ids and weights into rank r's buffer (the logits area of the buffer holds ids int32 [T, k], then weights
-// f32 [T, k]), all warps store the row itself.  The last CTA to finish raises the flags, waits for every
-// rank's, and sorts.
+// grid (row groups, world), kRouteThreads threads, dynamic shared memory of route_smem_bytes(R, slots, kRouteThreads)
+// bytes.
+// CTA (x, r): rows x, x + gridDim.x, ... of this rank's block go to rank r's buffer.  The warps of the CTA share the
+// routing of those rows (a warp per row: its k ids and weights are stored into the logits area of the buffer, which
+// holds ids int32 [T, k], then weights f32 [T, k]), then all warps store the rows themselves.  The last CTA to
+// finish raises the flags, waits for every rank's, and sorts with all of its warps.
 template <int PER>
-__global__ void __launch_bounds__(256) okc_ep_push_route_sort(const EpParams p, const RouteParams rp) {
+__global__ void __launch_bounds__(kRouteThreads, 1) okc_ep_push_route_sort(const EpParams p, const RouteParams rp) {
   extern __shared__ int32_t sm[];
   griddep_wait();
   griddep_launch_dependents();   // the gather kernel may set itself up; it waits for this grid to complete
@@ -264,13 +265,15 @@ __global__ void __launch_bounds__(256) okc_ep_push_route_sort(const EpParams p, 
   const int hv = p.H / 8;        // 16-byte vectors per hidden row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k = rp.k;
+  int32_t* ids_base = reinterpret_cast<int32_t*>(dest + p.off_logits);
+  float* wts_base = reinterpret_cast<float*>(dest + p.off_logits + static_cast<size_t>(p.tokens) * k * 4);
+  for (int row = blockIdx.x + warp * gridDim.x; row < tb; row += gridDim.x * (kRouteThreads / 32)) {
+    const size_t t = static_cast<size_t>(p.rank) * tb + row;
+    topk_token<PER>(p.logits_own + static_cast<size_t>(row) * p.E, 1, 0, p.E, k, 0, 1.0f, nullptr, lane, ids_base + t * k,
+                    wts_base + t * k);
+  }
   for (int row = blockIdx.x; row < tb; row += gridDim.x) {
     const size_t t = static_cast<size_t>(p.rank) * tb + row;
-    if (warp == 0) {
-      int32_t* ids_d = reinterpret_cast<int32_t*>(dest + p.off_logits) + t * k;
-      float* wts_d = reinterpret_cast<float*>(dest + p.off_logits + static_cast<size_t>(p.tokens) * k * 4) + t * k;
-      topk_token<PER>(p.logits_own + static_cast<size_t>(row) * p.E, 1, 0, p.E, k, 0, 1.0f, nullptr, lane, ids_d, wts_d);
-    }
     const uint4* hs = reinterpret_cast<const uint4*>(p.hidden_own + static_cast<size_t>(row) * p.hidden_stride);
     uint4* hd = reinterpret_cast<uint4*>(dest + p.off_hidden) + t * hv;
     for (int i = threadIdx.x; i < hv; i += blockDim.x) hd[i] = hs[i];
@@ -301,7 +304,7 @@ __global__ void __launch_bounds__(256) okc_ep_push_route_sort(const EpParams p, 
     ctrl[kEpCtrlSeqIn] = seq;
   }
   // the ids and weights of all tokens are in this rank's buffer now
-  sort_routes_cta<256>(rp, sm);
+  sort_routes_cta<kRouteThreads>(rp, sm);
 }
 
 cudaError_t launch_ep_push_route_sort(const EpParams& p, const RouteParams& rp, cudaStream_t stream) {
@@ -309,8 +312,8 @@ cudaError_t launch_ep_push_route_sort(const EpParams& p, const RouteParams& rp, 
   int gx = 128 / p.world;
   if (gx < 1) gx = 1;
   if (gx > tb) gx = tb;
-  const size_t smem = route_smem_bytes(rp.T * rp.kk, rp.slots, 256);
-  const dim3 grid(gx, p.world), block(256);
+  const size_t smem = route_smem_bytes(rp.T * rp.kk, rp.slots, kRouteThreads);
+  const dim3 grid(gx, p.world), block(kRouteThreads);
   cudaError_t e;
   if (p.E <= 128) {
     e = cudaFuncSetAttribute(okc_ep_push_route_sort<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

@@ -13,7 +13,6 @@
 namespace okc {
 
 
-constexpr int kRouteThreads = 1024;
 
 #ifdef OKC_WAIT_PROFILE
 extern "C" int okc_moe_debug_route_profile(long long* host_out) {

@@ -14,6 +14,8 @@ static __device__ long long g_route_prof[8];
 #define OKC_ROUTE_MARK(i)
 #endif
 
+constexpr int kRouteThreads = 1024;    // threads of a CTA that sorts a step's routes
+
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
 __device__ __forceinline__ int items_of(int c, bool wide_step, int chunk) {
@@ -212,15 +214,22 @@ __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* s
 
   OKC_ROUTE_MARK(4)
   // ---- 5. work items: experts by load descending (ties by id), cut into runs of item_rows() rows
+  // (rank of an expert = experts ahead of it; eight neighbouring lanes share one expert's comparisons)
   int active = 0;
-  for (int e = tid; e < p.slots; e += kThreads) {
-    const int c = cnt[e];
+  for (int base = 0; base < p.slots; base += kThreads / 8) {
+    const int e = base + (tid >> 3), sub = tid & 7;
+    const int c = (e < p.slots) ? cnt[e] : 0;
+    int rank = 0;
     if (c > 0) {
-      int rank = 0;
-      for (int o = 0; o < p.slots; ++o) {
+      for (int o = sub; o < p.slots; o += 8) {
         const int co = cnt[o];
         rank += (co > c || (co == c && o < e)) ? 1 : 0;
       }
+    }
+    rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+    rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+    rank += __shfl_xor_sync(0xffffffffu, rank, 4);
+    if (c > 0 && sub == 0) {
       order[rank] = e;
       ++active;
     }
