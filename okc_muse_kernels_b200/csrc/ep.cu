@@ -47,6 +47,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// Optional time stamps of a step's exchange kernels (-DOKC_WAIT_PROFILE), in nanoseconds of the GPU's global timer:
+// 0 exchange kernel starts (CTA 0, 0), 1 its last CTA has seen all own rows stored and fenced, 2 all ranks' flags seen,
+// 3 sort done; 4 combine + reduce kernel starts (CTA 0, 0: the GEMM launch before it is complete), 5 this rank's partial
+// sums published, 6 an own-row CTA has seen all ranks' partial sums, 7 the kernel's last CTA leaves.
+#ifdef OKC_WAIT_PROFILE
+static __device__ unsigned long long g_ep_marks[8];
+#define OKC_EP_MARK(i) { if (threadIdx.x == 0) g_ep_marks[i] = global_ns(); }
+#else
+#define OKC_EP_MARK(i) {}
+#endif
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -148,10 +158,16 @@ __global__ void __launch_bounds__(256) okc_ep_pull_reduce(const EpParams p) {
   const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (col < p.H) {
     const size_t off = (static_cast<size_t>(p.rank) * tb + row) * p.H + col;
+    // rank order: the same sum on every run; eight ranks' rows are requested before the first of their adds
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < p.world; ++r) {       // rank order: the same sum on every run
-      const float4 v = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r] + p.off_partial) + off);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    for (int r0 = 0; r0 < p.world; r0 += 8) {
+      float4 part[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (r0 + j < p.world) part[j] = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r0 + j] + p.off_partial) + off);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (r0 + j < p.world) { acc.x += part[j].x; acc.y += part[j].y; acc.z += part[j].z; acc.w += part[j].w; }
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
     uint2 o;
@@ -183,6 +199,7 @@ __global__ void __launch_bounds__(256) okc_ep_pull_reduce(const EpParams p) {
 // advance the step count (every CTA has read it by then).
 __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, const CombineParams c) {
   griddep_wait();    // y comes from the GEMM launch before
+  if (blockIdx.x == 0 && blockIdx.y == 0) OKC_EP_MARK(4)
   clear_call_state(c);
   uint8_t* mine = p.peer[p.rank];
   int32_t* ctrl = ctrl_of(mine);
@@ -200,7 +217,8 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
   if (!own) {
     if (live)
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(mine + p.off_partial) + static_cast<size_t>(t) * p.H + col) = acc;
-    __threadfence_system();
+    // (device scope: the rows are in this GPU's own memory, the CTA that raises the flag fences at system scope)
+    __threadfence();
     __syncthreads();
     __shared__ int s_last;
     if (threadIdx.x == 0) {
@@ -212,6 +230,7 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
       // every publishing CTA of this rank has stored (and fenced) its rows
       __threadfence_system();
       if (threadIdx.x < p.world) st_release_sys(flags_rs_of(p.peer[threadIdx.x]) + p.rank, seq);
+      OKC_EP_MARK(5)
     }
   } else {
     if (threadIdx.x < p.world && threadIdx.x != p.rank) {
@@ -221,13 +240,25 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
       }
     }
     __syncthreads();
+    if (blockIdx.x == 0 && t == own_t0) OKC_EP_MARK(6)
     if (live) {
       const size_t off = static_cast<size_t>(t) * p.H + col;
+      // all ranks' rows are requested before the first add (a load per add would put a trip over NVLink between
+      // every two adds); the adds run in rank order: the same sum on every run
       float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < p.world; ++r) {       // rank order: the same sum on every run
-        float4 v = acc;
-        if (r != p.rank) v = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r] + p.off_partial) + off);
-        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      for (int r0 = 0; r0 < p.world; r0 += 8) {      // eight ranks' rows in flight at a time
+        float4 part[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (r0 + j < p.world && r0 + j != p.rank)
+            part[j] = ld_relaxed_sys_f4(reinterpret_cast<const float*>(p.peer[r0 + j] + p.off_partial) + off);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (r0 + j < p.world) {
+            const float4 v = (r0 + j == p.rank) ? acc : part[j];
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+          }
+        }
       }
       __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
       uint2 o;
@@ -240,6 +271,7 @@ __global__ void __launch_bounds__(256) okc_ep_combine_reduce(const EpParams p, c
   if (threadIdx.x == 0) {
     const int total = gridDim.x * gridDim.y;
     if (atomicAdd(&ctrl[kEpCtrlDoneAll], 1) == total - 1) {
+      OKC_EP_MARK(7)
       ctrl[kEpCtrlDoneRs] = 0;
       ctrl[kEpCtrlDoneAll] = 0;
       ctrl[kEpCtrlSeqRs] = seq;
@@ -259,6 +291,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_ep_push_route_sort(const
   extern __shared__ int32_t sm[];
   griddep_wait();
   griddep_launch_dependents();   // the gather kernel may set itself up; it waits for this grid to complete
+  if (blockIdx.x == 0 && blockIdx.y == 0) OKC_EP_MARK(0)
   uint8_t* mine = p.peer[p.rank];
   uint8_t* dest = p.peer[blockIdx.y];
   const int tb = p.tokens / p.world;
@@ -288,6 +321,7 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_ep_push_route_sort(const
   }
   __syncthreads();
   if (!s_last) return;
+  OKC_EP_MARK(1)
   // every CTA of this rank has stored (and fenced) its rows: tell everybody, then wait for everybody
   __threadfence_system();
   const int32_t seq = ctrl[kEpCtrlSeqIn] + 1;
@@ -303,8 +337,11 @@ __global__ void __launch_bounds__(kRouteThreads, 1) okc_ep_push_route_sort(const
     ctrl[kEpCtrlDoneIn] = 0;
     ctrl[kEpCtrlSeqIn] = seq;
   }
+  OKC_EP_MARK(2)
   // the ids and weights of all tokens are in this rank's buffer now
   sort_routes_cta<kRouteThreads>(rp, sm);
+  __syncthreads();
+  OKC_EP_MARK(3)
 }
 
 cudaError_t launch_ep_push_route_sort(const EpParams& p, const RouteParams& rp, cudaStream_t stream) {
@@ -358,6 +395,13 @@ cudaError_t launch_ep_reduce(const EpParams& p, cudaStream_t stream) {
   okc_ep_pull_reduce<<<dim3((p.H + 1023) / 1024, tb), 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
+
+#ifdef OKC_WAIT_PROFILE
+// host_out: unsigned long long [8], the stamps of the last step on the current device
+extern "C" int okc_ep_debug_marks(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_ep_marks, sizeof(g_ep_marks)) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 cudaError_t launch_ep_combine_reduce(const EpParams& p, const CombineParams& c, cudaStream_t stream) {
   return launch_kernel(okc_ep_combine_reduce, dim3((p.H + 1023) / 1024, p.tokens), dim3(256), 0, stream, true, p, c);
