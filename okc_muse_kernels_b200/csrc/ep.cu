@@ -401,6 +401,10 @@ cudaError_t launch_ep_reduce(const EpParams& p, cudaStream_t stream) {
 extern "C" int okc_ep_debug_marks(unsigned long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, g_ep_marks, sizeof(g_ep_marks)) == cudaSuccess ? 0 : -3;
 }
+// host_out: long long [8], the SM clock of thread 0 at the end of each phase of the sort inside the exchange kernel
+extern "C" int okc_ep_debug_sort_phases(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_route_prof, sizeof(g_route_prof)) == cudaSuccess ? 0 : -3;
+}
 #endif
 
 cudaError_t launch_ep_combine_reduce(const EpParams& p, const CombineParams& c, cudaStream_t stream) {
