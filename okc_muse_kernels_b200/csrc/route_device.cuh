@@ -54,7 +54,7 @@ __device__ __forceinline__ void topk_token(const float* __restrict__ row, int n_
     } else {
       sc[j] = x;
     }
-    v[j] = (x == x) ? x : -INFINITY;
+    v[j] = (x == x) ? (x == 0.0f ? 0.0f : x) : -INFINITY;   // NaN never wins; -0 and +0 are one key
   }
   uint32_t taken = 0;
   float bv = -INFINITY, bs = 0.f;
@@ -67,15 +67,13 @@ __device__ __forceinline__ void topk_token(const float* __restrict__ row, int n_
   float my_val = 0.f;
   int my_id = 0;
   for (int r = 0; r < k; ++r) {
-    float wv = bv, wsc = bs;
-    int wi = bi;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
-      const float os = __shfl_xor_sync(0xffffffffu, wsc, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
-      if (better(ov, oi, wv, wi)) { wv = ov; wi = oi; wsc = os; }
-    }
+    // warp arg-max in three warp-wide operations: the largest key (floats mapped to integers of the same order), then
+    // the lowest expert id among the lanes that hold it, then that lane's score (expert e sits in lane e % 32)
+    const uint32_t bits = __float_as_uint(bv);
+    const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
+    const int wi = static_cast<int>(__reduce_min_sync(0xffffffffu, key == kmax ? static_cast<uint32_t>(bi) : 0x7fffffffu));
+    const float wsc = __shfl_sync(0xffffffffu, bs, wi & 31);
     if (lane == r) { my_val = wsc; my_id = wi; }
     if (wi == bi) {
       // this lane held the winner: next best of what it has left
