@@ -612,11 +612,6 @@ def run_gpu(args):
     m = measure(wl, tokens, args, dev, world, rank, max_tokens=max(synth.C3_TOKENS) if args.sweep else None)
     failed = m["parity"] is not None and not m["parity"]["ok"]
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        h, lg = m["inputs0"]
-        cpu = _cpu_baseline(wl, tokens, h, lg, m["bytes_seed0"], dev)
-
     extra = {}
     if world == 1 and args.workload is None and args.tokens is None and not args.no_c4_anchor and not args.sweep:
         # configuration 4 on this one GPU (all 256 experts + the shared expert local, no exchange): the
@@ -630,6 +625,11 @@ def run_gpu(args):
                           "unit": UNIT, "touched_experts_per_seed": a["touched"], "gemm_ms": a["roofline"]["kernel_ms"]["gemm"],
                           "frac_of_peak": a["roofline"]["step_frac_of_peak"], "parity": a["parity"]}
         failed = failed or not a["parity"]["ok"]
+    # (the host-core baseline after every GPU measurement of the run: its threads keep the host busy for a while)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        h, lg = m["inputs0"]
+        cpu = _cpu_baseline(wl, tokens, h, lg, m["bytes_seed0"], dev)
     if args.sweep:
         # configuration 3: the batch sweep on configuration 2's weights, one entry per T
         rows = []
@@ -641,16 +641,17 @@ def run_gpu(args):
             failed = failed or not a["parity"]["ok"]
         extra["sweep"] = rows
 
-    # kernels of this library per step.  One GPU: top-k + sort (one kernel up to 32 tokens, else two), gather, the
+    # kernels of this library per step.  One GPU: top-k + sort (one kernel), gather (steps of more than 8 tokens), the
     # GEMM launch, combine, + the router's logits kernel with --route-from-hidden.  Expert parallel, peer
-    # exchange: push + router + sort (one kernel), gather, GEMMs, combine + reduce-scatter; the NCCL exchange:
-    # the single-GPU kernels + the cast.
+    # exchange: push + router + sort (one kernel; or push, then top-k + sort), gather, GEMMs, combine + reduce-scatter
+    # (or combine, then reduce); the NCCL exchange: the single-GPU kernels + the cast.
     layer = m["layer"]
-    single = (1 if tokens <= 32 else 2) + 3 + (1 if args.route_from_hidden else 0)
+    gather = 0 if tokens <= 8 else 1
+    single = 1 + gather + 2 + (1 if args.route_from_hidden else 0)
     if world == 1:
         launches_per_step = single
     elif layer.exchange == "peer":
-        launches_per_step = (1 if layer.route_in_gather else 1 + (1 if tokens <= 32 else 2)) + 2 + (1 if layer.fuse_combine else 1)
+        launches_per_step = (1 if layer.route_in_gather else 2) + gather + 1 + (1 if layer.fuse_combine else 2)
     else:
         launches_per_step = single + 1
     if rank == 0:
