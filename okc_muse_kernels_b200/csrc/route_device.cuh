@@ -111,18 +111,22 @@ template <int kThreads>
 __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* sm) {
   const int R = p.T * p.kk;
   // shared memory: rexp int32 [R] (local expert slot or -1) | whist int32 [32][slots] | order int32 [slots]
-  // | cnt int32 [slots+1] | offs int32 [slots+1] | ibase int32 [slots+1]
+  // | cnt int32 [slots+1] | offs int32 [slots+1] | ibase int32 [slots+1] | rwt f32 [R]
   int32_t* rexp = sm;
   int32_t* whist = rexp + R;
   int32_t* order = whist + (kThreads / 32) * p.slots;
   int32_t* cnt = order + p.slots;
   int32_t* offs = cnt + p.slots + 1;
   int32_t* ibase = offs + p.slots + 1;
+  float* rwt = reinterpret_cast<float*>(ibase + p.slots + 1);     // f32 [R]: the routes' weights
   __shared__ int s_nact;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) s_nact = 0;
   OKC_ROUTE_MARK(0)
+  // (asked for here, used by the thread that writes the step's control words at the end: the trip to L2 is over by then)
+  int router_gave_up = 0;
+  if (tid == 31) router_gave_up = p.meta[kMetaRouterStatus];
 
   for (int i = tid; i < (kThreads / 32) * p.slots; i += kThreads) whist[i] = 0;
   for (int i = tid; i < R; i += kThreads) p.sorted[i] = -1;
@@ -131,11 +135,14 @@ __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* s
   for (int i = tid; i < p.T * p.k; i += kThreads) {
     const int t = i / p.k, sl = i - t * p.k;
     const int le = __ldcg(p.ids_in + i) - p.local_start;
+    rwt[t * p.kk + sl] = __ldcg(p.wts_in + i);
     rexp[t * p.kk + sl] = (le >= 0 && le < p.local_count) ? le : -1;
   }
   if (p.has_shared)
-    for (int t = tid; t < p.T; t += kThreads)
+    for (int t = tid; t < p.T; t += kThreads) {
       rexp[t * p.kk + p.k] = (t >= p.own_t0 && t < p.own_t1) ? p.local_count : -1;
+      rwt[t * p.kk + p.k] = 1.0f;
+    }
   __syncthreads();
   OKC_ROUTE_MARK(1)
 
@@ -195,12 +202,9 @@ __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* s
     if (i < R) {
       if (e >= 0) {
         const int q = offs[e] + whist[warp * p.slots + e] + __popc(m & ((1u << lane) - 1u));
-        const int t = i / p.kk, s = i - t * p.kk;
-        float w = 1.0f;
-        if (s < p.k) w = __ldcg(p.wts_in + t * p.k + s);
         p.pos[i] = q;
         p.sorted[q] = i;
-        p.wsorted[q] = w;
+        p.wsorted[q] = rwt[i];
       } else {
         p.pos[i] = -1;
       }
@@ -276,7 +280,6 @@ __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* s
       p.meta[kMetaItems] = incl < p.max_items ? incl : p.max_items;
       p.meta[kMetaLocalRoutes] = offs[p.slots];
       // a new step: clean status words, unless the router-logits kernel of this very step gave up
-      const int router_gave_up = p.meta[kMetaRouterStatus];
       p.meta[kMetaStatus] = router_gave_up ? OKC_ERR_TIMEOUT : 0;
       p.meta[kMetaDetail] = router_gave_up;
       p.meta[kMetaRouterStatus] = 0;
@@ -305,7 +308,7 @@ __device__ __forceinline__ void sort_routes_cta(const RouteParams& p, int32_t* s
 }
 
 inline size_t route_smem_bytes(int R, int slots, int threads) {
-  return sizeof(int32_t) * (static_cast<size_t>(R) + static_cast<size_t>(threads / 32) * slots + slots + 3 * (slots + 1));
+  return sizeof(int32_t) * (2 * static_cast<size_t>(R) + static_cast<size_t>(threads / 32) * slots + slots + 3 * (slots + 1));
 }
 
 }  // namespace okc
