@@ -87,6 +87,23 @@ def router_scores(hidden_bf16: np.ndarray, router_w: np.ndarray, bias: np.ndarra
     return scores, biased, logits
 
 
+def router_split(router_w: np.ndarray):
+    """The FP32 router matrix as two bf16 matrices (uint16 bit patterns), w ~ hi + lo with hi = bf16(w) and
+    lo = bf16(w - hi): what the reference prepares for its tensor-core router (the ``w`` / ``wlo`` operands of
+    ``_router_split``, muse_decode_layer/layer.py:325-351)."""
+    w = np.asarray(router_w, np.float32)
+    hi = f32_to_bf16(w)
+    lo = f32_to_bf16(w - bf16_to_f32(hi))
+    return hi, lo
+
+
+def router_logits_hilo(hidden_bf16: np.ndarray, hi: np.ndarray, lo: np.ndarray) -> np.ndarray:
+    """Logits of the split router: h . hi^T + h . lo^T with exact bf16 products, summed in float64 (the kernel
+    accumulates the same products in FP32)."""
+    h = bf16_to_f32(np.asarray(hidden_bf16)).astype(np.float64)
+    return h @ bf16_to_f32(hi).astype(np.float64).T + h @ bf16_to_f32(lo).astype(np.float64).T
+
+
 # tolerances of the reference's routing checker (muse_decode_layer/reference.py:68-76)
 ROUTE_TOL = 5e-2
 LOCAL_SLACK = (0.08, 4)

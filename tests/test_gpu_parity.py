@@ -426,6 +426,9 @@ def test_route_from_hidden_states_matches_the_layer_router(T, H, E, k, mode, ten
     if tensor_cores:
         hi, lo = rw[:E].float().cpu(), rw[E:].float().cpu()
         assert (hi + lo - router_w).abs().max() <= router_w.abs().max() * 2.0 ** -15      # w = hi + lo to 16 bits or so
+        ohi, olo = moe_np.router_split(router_w.numpy())                                  # the oracle's split, bit for bit
+        assert np.array_equal(rw[:E].cpu().view(torch.uint16).numpy(), ohi)
+        assert np.array_equal(rw[E:].cpu().view(torch.uint16).numpy(), olo)
     ids, wts = okc.route_hidden(hidden.to(dev), rw, state, bias=None if bias is None else bias.to(dev), mode=mode)
     rc, detail = okc.read_status(state)
     assert rc == 0, f"device status {rc} detail {detail:#x}"

@@ -233,3 +233,18 @@ def test_reference_arm_of_the_bench_runs_on_host_cores():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert line["config"]["workload"].startswith("c1")
+
+
+def test_oracle_router_split_keeps_sixteen_bits_of_the_matrix():
+    """w = hi + lo to about 2^-16 relative; the logits of the split router agree with the float64 logits of the
+    FP32 matrix far inside the routing checker's tolerance."""
+    rng = np.random.default_rng(11)
+    T, H, E = 16, 512, 64
+    hidden = moe_np.f32_to_bf16(rng.standard_normal((T, H)).astype(np.float32))
+    w = (rng.standard_normal((E, H)) / 16).astype(np.float32)
+    hi, lo = moe_np.router_split(w)
+    back = moe_np.bf16_to_f32(hi).astype(np.float64) + moe_np.bf16_to_f32(lo).astype(np.float64)
+    assert np.abs(back - w).max() <= np.abs(w).max() * 2.0 ** -15
+    _, _, logits = moe_np.router_scores(hidden, w)
+    split = moe_np.router_logits_hilo(hidden, hi, lo)
+    assert np.abs(split - logits).max() <= 2e-5 * max(1.0, float(np.abs(logits).max()))
