@@ -8,8 +8,11 @@
 //
 // One persistent CTA per SM, 29 warps:
 //   warp 28       producer: one bulk copy of the 36 KB FP4 stage image + 2-D TMA tiles of the
-//                 token operand (128-byte swizzle) per stage, mbarrier ring
-//   warps 0..7    MMA issuers, one thread each.  A thread needs 100+ cycles to issue one
+//                 token operand (128-byte swizzle) per stage, mbarrier ring.  The whole warp runs
+//                 the loop; lane 0 takes the units and starts the weight copies, the token copies
+//                 of a stage start from as many lanes at once (steps of up to 8 tokens: a copy per
+//                 row straight from the caller's array, no gathered copy of the rows)
+//   warps 0..7    MMA issuers, whole warps running the loops, one elected lane issuing.  A thread needs 100+ cycles to issue one
 //                 tcgen05.mma whatever its N (more when its warp competes for issue slots), and
 //                 issue from several warps overlaps, so the 32 MMAs of a narrow item's stage are
 //                 spread over eight issuers: (tile of the pair) x (64-wide K block of the stage).
