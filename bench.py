@@ -2,6 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c1|c4|c5] [--tokens T]
     python bench.py --sweep            # configuration 3: one line per batch size T = 1 ... 256
+    python bench.py --route-from-hidden [fma|mma]   # the router logits computed from the token rows inside the step
 
 N = 1: configuration 2 (T=32, H=4096, I=1536, E=128, top-8, all experts on the GPU); the line also
 carries `c4_n1`, configuration 4 on this one GPU, as the anchor of the 1 -> 8 GPU curve.
